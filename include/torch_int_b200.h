@@ -1,0 +1,178 @@
+/* C ABI of libtorch_int_b200.so: the W8A8 operator set of torch-int for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes raw DEVICE pointers of the CURRENT CUDA device,
+ * sizes as int64_t, scalars as float and a cudaStream_t passed as void*
+ * (NULL = the legacy default stream).  Nothing is allocated, nothing
+ * synchronises, outputs are written in place by kernels enqueued on `stream`.
+ * Return value: 0 on success, negative on error (TI_E_*); the message of the
+ * last error of the calling thread is returned by ti_last_error().
+ *
+ * The ops mirror, one to one, the functions the reference exports from its
+ * pybind11 module `torch_int._CUDA` (torch_int/kernels/bindings.cpp:5-20); the
+ * citation on each declaration is the reference function it replaces.  Tensor
+ * arguments of the reference become (pointer, sizes); the output tensor the
+ * reference allocates and returns becomes a caller-provided `out` pointer.
+ *
+ * Shape rules (the same ones the reference kernels impose through their
+ * 128-bit vector accesses): K % 16 == 0; N % 16 == 0 for int8 outputs and
+ * N % 4 == 0 for int32 / fp32 outputs; all pointers 16-byte aligned.  M (rows)
+ * and the batch count are arbitrary, including 0 (no-op) and 1.
+ */
+#ifndef TORCH_INT_B200_H
+#define TORCH_INT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TI_OK 0
+#define TI_E_INVALID (-1) /* bad shape, alignment or pointer */
+#define TI_E_CUDA (-2)    /* a CUDA runtime / driver call failed */
+#define TI_E_DEVICE (-3)  /* a kernel's bounded wait gave up (see ti_device_status) */
+
+/* ---- linear layers: out[M,N] = epilogue(input[M,K] . weight[N,K]^T, bias[N]) ---- */
+
+/* int8 out = sat_rne(fma(alpha, float(acc), beta * float(bias))), bias int8.
+ * Replaces linear_a8_w8_b8_o8 (torch_int/kernels/linear.cu:369-473). */
+int ti_linear_a8_w8_b8_o8(const int8_t* input, const int8_t* weight, const int8_t* bias,
+                          int8_t* out, int64_t M, int64_t N, int64_t K, float alpha, float beta,
+                          void* stream);
+
+/* Same with max(., 0) before rounding.
+ * Replaces linear_relu_a8_w8_b8_o8 (torch_int/kernels/linear.cu:476-625). */
+int ti_linear_relu_a8_w8_b8_o8(const int8_t* input, const int8_t* weight, const int8_t* bias,
+                               int8_t* out, int64_t M, int64_t N, int64_t K, float alpha,
+                               float beta, void* stream);
+
+/* fp32 out = fma(alpha, float(acc), beta * bias), bias fp32.
+ * Replaces linear_a8_w8_bfp32_ofp32 (torch_int/kernels/linear.cu:246-365). */
+int ti_linear_a8_w8_bfp32_ofp32(const int8_t* input, const int8_t* weight, const float* bias,
+                                float* out, int64_t M, int64_t N, int64_t K, float alpha,
+                                float beta, void* stream);
+
+/* int32 out = acc + bias (two's-complement wrap), bias int32.
+ * Replaces linear_a8_w8_b32_o32 (torch_int/kernels/linear.cu:13-136). */
+int ti_linear_a8_w8_b32_o32(const int8_t* input, const int8_t* weight, const int32_t* bias,
+                            int32_t* out, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* int32 out = sat_rne(fma(alpha, float(acc), beta * float(bias))), bias int32.
+ * Replaces linear_a8_w8_b32_o32_with_scaling (torch_int/kernels/linear.cu:139-243). */
+int ti_linear_a8_w8_b32_o32_with_scaling(const int8_t* input, const int8_t* weight,
+                                         const int32_t* bias, int32_t* out, int64_t M, int64_t N,
+                                         int64_t K, float alpha, float beta, void* stream);
+
+/* ---- batched products: C[b] = epilogue(A[b][M,K] . B[b][N,K]^T), packed tensors ---- */
+
+/* fp32 C = alpha * float(acc).
+ * Replaces bmm_s8t_s8n_f32t (torch_int/kernels/bmm.cu:10-108). */
+int ti_bmm_s8t_s8n_f32t(const int8_t* A, const int8_t* B, float* C, int64_t batch, int64_t M,
+                        int64_t N, int64_t K, float alpha, void* stream);
+
+/* int8 C = sat_rne(alpha * float(acc)).
+ * Replaces bmm_s8t_s8n_s8t (torch_int/kernels/bmm.cu:110-208). */
+int ti_bmm_s8t_s8n_s8t(const int8_t* A, const int8_t* B, int8_t* C, int64_t batch, int64_t M,
+                       int64_t N, int64_t K, float alpha, void* stream);
+
+/* int32 C = acc.
+ * Replaces bmm_s8t_s8n_s32t (torch_int/kernels/bmm.cu:210-295). */
+int ti_bmm_s8t_s8n_s32t(const int8_t* A, const int8_t* B, int32_t* C, int64_t batch, int64_t M,
+                        int64_t N, int64_t K, void* stream);
+
+/* ---- strided form of all of the above ---- */
+
+/* Epilogue selector of ti_gemm_i8_ex. */
+enum ti_epilogue {
+  TI_EPI_S8_BIAS_S8 = 0,     /* ti_linear_a8_w8_b8_o8 */
+  TI_EPI_S8_BIAS_S8_RELU = 1, /* ti_linear_relu_a8_w8_b8_o8 */
+  TI_EPI_F32_BIAS_F32 = 2,   /* ti_linear_a8_w8_bfp32_ofp32 */
+  TI_EPI_S32_BIAS_S32_ADD = 3, /* ti_linear_a8_w8_b32_o32 */
+  TI_EPI_S32_BIAS_S32_SCALE = 4, /* ti_linear_a8_w8_b32_o32_with_scaling */
+  TI_EPI_F32_ALPHA = 5,      /* ti_bmm_s8t_s8n_f32t */
+  TI_EPI_S8_ALPHA = 6,       /* ti_bmm_s8t_s8n_s8t */
+  TI_EPI_S32_RAW = 7         /* ti_bmm_s8t_s8n_s32t */
+};
+
+/* A [batch2][batch][M][K], B [batch2][batch][N][K], C [batch2][batch][M][N];
+ * strides in ELEMENTS; K and N are the contiguous dimensions.  A zero batch
+ * stride broadcasts the operand.  Operand strides must be multiples of 16,
+ * output strides multiples of 16 (int8 out) or 4 (32-bit out). */
+typedef struct ti_gemm_desc {
+  const int8_t* A;
+  const int8_t* B;
+  void* C;
+  const void* bias; /* N elements, type per epilogue; NULL when the epilogue has no bias */
+  int64_t M, N, K;
+  int64_t batch, batch2;
+  int64_t lda, ldb, ldc;
+  int64_t strideA, strideB, strideC;
+  int64_t stride2A, stride2B, stride2C;
+  float alpha, beta;
+  int32_t epilogue; /* enum ti_epilogue */
+  int32_t tile_n;   /* 0 = automatic; else 32, 64, 128 or 256 */
+} ti_gemm_desc;
+
+/* The reference has no strided entry point: its wrappers assume packed tensors
+ * (torch_int/kernels/linear.cu:429-434, bmm.cu:18-20,71-73) and the attention
+ * module makes contiguous copies to satisfy that (torch_int/models/opt.py:80-81,
+ * 180,191-196).  This form lets a caller skip those copies. */
+int ti_gemm_i8_ex(const ti_gemm_desc* desc, void* stream);
+
+/* ---- LayerNorm-quantise ops ---- */
+
+/* (residual_out, q) = dq_add_layernorm_q(input int32, input_scale, residual, gamma, beta, eps):
+ *   residual_out = residual + input_scale * float(input)   (one fused multiply-add)
+ *   q = int8(rne(clamp(LayerNorm(residual_out) * gamma + beta, -128, 127)))
+ * rows x H row-major tensors; gamma, beta fp32 [H].  residual_is_half: 0 = fp32
+ * residual / residual_out, 1 = fp16.
+ * Replaces dq_add_layernorm_q (torch_int/kernels/fused.cu:7-25), which issues
+ * five ATen kernels. */
+int ti_dq_add_layernorm_q(const int32_t* input, float input_scale, const void* residual,
+                          int residual_is_half, const float* gamma, const float* beta, float eps,
+                          void* residual_out, int8_t* q, int64_t rows, int64_t H, void* stream);
+
+/* Same with an fp32 bias vector [H] applied to the dequantised input first:
+ *   residual_out = residual + fma(input_scale, float(input), input_bias).
+ * No reference counterpart: used when `input` is an int32 accumulator summed
+ * across tensor-parallel ranks, so that the bias of the row-parallel linear
+ * (torch_int/nn/linear.py:213-214) is added once, after the reduction. */
+int ti_dq_add_layernorm_q_bias(const int32_t* input, float input_scale, const float* input_bias,
+                               const void* residual, int residual_is_half, const float* gamma,
+                               const float* beta, float eps, void* residual_out, int8_t* q,
+                               int64_t rows, int64_t H, void* stream);
+
+/* q = int8(clamp(rne(LayerNorm(x) * gamma + beta), -128, 127)); x fp32 (x_is_half=0)
+ * or fp16 (1), gamma/beta fp32.
+ * Replaces LayerNormQ.forward (torch_int/nn/fused.py:13-18), four ATen kernels. */
+int ti_layernorm_q(const void* x, int x_is_half, const float* gamma, const float* beta, float eps,
+                   int8_t* q, int64_t rows, int64_t H, void* stream);
+
+/* probs int8 [batch_heads, T, S] = rne(127 * softmax(max(scores + mask, -FLT_MAX))) row-wise.
+ * scores fp32 with row stride lds; mask: optional additive fp32 [batch_heads/heads, T, S]
+ * (the reference's [bsz, 1, tgt, src] mask) or NULL; causal >= 0 generates the mask
+ * "column j of row t is visible iff j <= t + causal" instead; causal < 0: none.
+ * Replaces the mask / softmax / *127 / round / int8 chain of Int8OPTAttention.forward
+ * (torch_int/models/opt.py:139-178), five to six ATen kernels. */
+int ti_softmax_q(const float* scores, const float* mask, int8_t* probs, int64_t batch_heads,
+                 int64_t heads, int64_t T, int64_t S, int64_t lds, int64_t ldp, int causal,
+                 void* stream);
+
+/* ---- status ---- */
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char* ti_last_error(void);
+
+/* Synchronises the current device and stores the kernel status word in *status:
+ * 0 = ok, else the code of the first in-kernel wait that ran into its time
+ * limit (the kernels never spin forever).  reset != 0 clears it. */
+int ti_device_status(int* status, int reset);
+
+/* ABI version of this header (bumped on incompatible changes). */
+int ti_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TORCH_INT_B200_H */

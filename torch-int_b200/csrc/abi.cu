@@ -1,0 +1,194 @@
+// extern "C" entry points of libtorch_int_b200.so (declared in
+// include/torch_int_b200.h).  Each one fills a GemmProblem or calls a row-kernel
+// launcher; nothing here allocates or synchronises.
+#include "../../include/torch_int_b200.h"
+
+#include "gemm_i8.h"
+#include "norm_quant.h"
+
+using namespace ti;
+
+namespace {
+
+int linear(const int8_t* x, const int8_t* w, const void* bias, void* out, int64_t M, int64_t N,
+           int64_t K, float alpha, float beta, int epi, void* stream) {
+  GemmProblem g;
+  g.A = x;
+  g.B = w;
+  g.C = out;
+  g.bias = bias;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.lda = K;
+  g.ldb = K;
+  g.ldc = N;
+  g.strideA = M * K;
+  g.strideB = N * K;
+  g.strideC = M * N;
+  g.stride2A = g.strideA;
+  g.stride2B = g.strideB;
+  g.stride2C = g.strideC;
+  g.alpha = alpha;
+  g.beta = beta;
+  g.epilogue = epi;
+  return launch_gemm_i8(g, static_cast<cudaStream_t>(stream));
+}
+
+int bmm(const int8_t* A, const int8_t* B, void* C, int64_t batch, int64_t M, int64_t N, int64_t K,
+        float alpha, int epi, void* stream) {
+  GemmProblem g;
+  g.A = A;
+  g.B = B;
+  g.C = C;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.batch = batch;
+  g.lda = K;
+  g.ldb = K;
+  g.ldc = N;
+  g.strideA = M * K;
+  g.strideB = N * K;
+  g.strideC = M * N;
+  g.stride2A = batch * g.strideA;
+  g.stride2B = batch * g.strideB;
+  g.stride2C = batch * g.strideC;
+  g.alpha = alpha;
+  g.epilogue = epi;
+  return launch_gemm_i8(g, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int ti_linear_a8_w8_b8_o8(const int8_t* input, const int8_t* weight, const int8_t* bias,
+                          int8_t* out, int64_t M, int64_t N, int64_t K, float alpha, float beta,
+                          void* stream) {
+  return linear(input, weight, bias, out, M, N, K, alpha, beta, EPI_S8_BIAS_S8, stream);
+}
+
+int ti_linear_relu_a8_w8_b8_o8(const int8_t* input, const int8_t* weight, const int8_t* bias,
+                               int8_t* out, int64_t M, int64_t N, int64_t K, float alpha,
+                               float beta, void* stream) {
+  return linear(input, weight, bias, out, M, N, K, alpha, beta, EPI_S8_BIAS_S8_RELU, stream);
+}
+
+int ti_linear_a8_w8_bfp32_ofp32(const int8_t* input, const int8_t* weight, const float* bias,
+                                float* out, int64_t M, int64_t N, int64_t K, float alpha,
+                                float beta, void* stream) {
+  return linear(input, weight, bias, out, M, N, K, alpha, beta, EPI_F32_BIAS_F32, stream);
+}
+
+int ti_linear_a8_w8_b32_o32(const int8_t* input, const int8_t* weight, const int32_t* bias,
+                            int32_t* out, int64_t M, int64_t N, int64_t K, void* stream) {
+  return linear(input, weight, bias, out, M, N, K, 1.f, 1.f, EPI_S32_BIAS_S32_ADD, stream);
+}
+
+int ti_linear_a8_w8_b32_o32_with_scaling(const int8_t* input, const int8_t* weight,
+                                         const int32_t* bias, int32_t* out, int64_t M, int64_t N,
+                                         int64_t K, float alpha, float beta, void* stream) {
+  return linear(input, weight, bias, out, M, N, K, alpha, beta, EPI_S32_BIAS_S32_SCALE, stream);
+}
+
+int ti_bmm_s8t_s8n_f32t(const int8_t* A, const int8_t* B, float* C, int64_t batch, int64_t M,
+                        int64_t N, int64_t K, float alpha, void* stream) {
+  return bmm(A, B, C, batch, M, N, K, alpha, EPI_F32_ALPHA, stream);
+}
+
+int ti_bmm_s8t_s8n_s8t(const int8_t* A, const int8_t* B, int8_t* C, int64_t batch, int64_t M,
+                       int64_t N, int64_t K, float alpha, void* stream) {
+  return bmm(A, B, C, batch, M, N, K, alpha, EPI_S8_ALPHA, stream);
+}
+
+int ti_bmm_s8t_s8n_s32t(const int8_t* A, const int8_t* B, int32_t* C, int64_t batch, int64_t M,
+                        int64_t N, int64_t K, void* stream) {
+  return bmm(A, B, C, batch, M, N, K, 1.f, EPI_S32_RAW, stream);
+}
+
+int ti_gemm_i8_ex(const ti_gemm_desc* d, void* stream) {
+  if (d == nullptr) {
+    set_error("ti_gemm_i8_ex: null descriptor");
+    return TI_E_INVALID;
+  }
+  if (d->epilogue < 0 || d->epilogue >= EPI_COUNT) {
+    set_error("ti_gemm_i8_ex: unknown epilogue %d", d->epilogue);
+    return TI_E_INVALID;
+  }
+  if (d->tile_n != 0 && d->tile_n != 32 && d->tile_n != 64 && d->tile_n != 128 && d->tile_n != 256) {
+    set_error("ti_gemm_i8_ex: tile_n must be 0, 32, 64, 128 or 256");
+    return TI_E_INVALID;
+  }
+  GemmProblem g;
+  g.A = d->A;
+  g.B = d->B;
+  g.C = d->C;
+  g.bias = d->bias;
+  g.M = d->M;
+  g.N = d->N;
+  g.K = d->K;
+  g.batch = d->batch;
+  g.batch2 = d->batch2;
+  g.lda = d->lda;
+  g.ldb = d->ldb;
+  g.ldc = d->ldc;
+  g.strideA = d->strideA;
+  g.strideB = d->strideB;
+  g.strideC = d->strideC;
+  g.stride2A = d->stride2A;
+  g.stride2B = d->stride2B;
+  g.stride2C = d->stride2C;
+  g.alpha = d->alpha;
+  g.beta = d->beta;
+  g.epilogue = d->epilogue;
+  g.force_bn = d->tile_n;
+  return launch_gemm_i8(g, static_cast<cudaStream_t>(stream));
+}
+
+int ti_dq_add_layernorm_q(const int32_t* input, float input_scale, const void* residual,
+                          int residual_is_half, const float* gamma, const float* beta, float eps,
+                          void* residual_out, int8_t* q, int64_t rows, int64_t H, void* stream) {
+  return dq_add_layernorm_q(input, input_scale, residual, residual_is_half, nullptr, gamma, beta, eps,
+                            residual_out, q, rows, H, static_cast<cudaStream_t>(stream));
+}
+
+int ti_dq_add_layernorm_q_bias(const int32_t* input, float input_scale, const float* input_bias,
+                               const void* residual, int residual_is_half, const float* gamma,
+                               const float* beta, float eps, void* residual_out, int8_t* q,
+                               int64_t rows, int64_t H, void* stream) {
+  if (input_bias == nullptr) {
+    set_error("ti_dq_add_layernorm_q_bias: null bias");
+    return TI_E_INVALID;
+  }
+  return dq_add_layernorm_q(input, input_scale, residual, residual_is_half, input_bias, gamma, beta,
+                            eps, residual_out, q, rows, H, static_cast<cudaStream_t>(stream));
+}
+
+int ti_layernorm_q(const void* x, int x_is_half, const float* gamma, const float* beta, float eps,
+                   int8_t* q, int64_t rows, int64_t H, void* stream) {
+  return layernorm_q(x, x_is_half, gamma, beta, eps, q, rows, H, static_cast<cudaStream_t>(stream));
+}
+
+int ti_softmax_q(const float* scores, const float* mask, int8_t* probs, int64_t batch_heads,
+                 int64_t heads, int64_t T, int64_t S, int64_t lds, int64_t ldp, int causal,
+                 void* stream) {
+  return softmax_q(scores, mask, probs, batch_heads, heads, T, S, lds, ldp, causal,
+                   static_cast<cudaStream_t>(stream));
+}
+
+const char* ti_last_error(void) { return last_error(); }
+
+int ti_device_status(int* status, int reset) {
+  if (status == nullptr) {
+    set_error("ti_device_status: null pointer");
+    return TI_E_INVALID;
+  }
+  return device_status(status, reset != 0);
+}
+
+int ti_abi_version(void) { return 1; }
+
+}  // extern "C"
+#pragma GCC visibility pop

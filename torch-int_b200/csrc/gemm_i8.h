@@ -1,0 +1,54 @@
+// Host-side description of one (batched) int8 x int8 -> int32 contraction with
+// a fused epilogue, and the launcher that runs it on the current device.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/torch_int_b200.h"  // TI_OK / TI_E_* status codes
+
+namespace ti {
+
+// Epilogue kinds.  acc = sum_k A[m,k] * B[n,k] in int32; a = float(acc) (RN).
+// The float forms compute t = beta * float(bias[n]) (one rounding) and then
+// y = fma(alpha, a, t) (one rounding); the *_ALPHA forms compute y = alpha * a.
+enum Epilogue : int {
+  EPI_S8_BIAS_S8 = 0,      // int8  out = sat_rne(y),            bias int8
+  EPI_S8_BIAS_S8_RELU,     // int8  out = sat_rne(max(y, 0)),    bias int8
+  EPI_F32_BIAS_F32,        // fp32  out = y,                     bias fp32
+  EPI_S32_BIAS_S32_ADD,    // int32 out = acc + bias (wraps),    bias int32
+  EPI_S32_BIAS_S32_SCALE,  // int32 out = sat_rne(y),            bias int32
+  EPI_F32_ALPHA,           // fp32  out = alpha * a
+  EPI_S8_ALPHA,            // int8  out = sat_rne(alpha * a)
+  EPI_S32_RAW,             // int32 out = acc
+  EPI_COUNT
+};
+
+// A is [batch2, batch, M, K], B is [batch2, batch, N, K], C is
+// [batch2, batch, M, N]; all strides are in elements, K and N are contiguous.
+struct GemmProblem {
+  const int8_t* A = nullptr;
+  const int8_t* B = nullptr;
+  void* C = nullptr;
+  const void* bias = nullptr;  // N elements (type per epilogue) or nullptr
+  int64_t M = 0, N = 0, K = 0;
+  int64_t batch = 1, batch2 = 1;
+  int64_t lda = 0, ldb = 0, ldc = 0;
+  int64_t strideA = 0, strideB = 0, strideC = 0;     // per `batch` index
+  int64_t stride2A = 0, stride2B = 0, stride2C = 0;  // per `batch2` index
+  float alpha = 1.f, beta = 0.f;
+  int epilogue = EPI_S32_RAW;
+  int force_bn = 0;  // 0 = choose the N tile automatically
+};
+
+// Returns 0 or a negative TI_E_* code (message via set_error()).
+int launch_gemm_i8(const GemmProblem& p, cudaStream_t stream);
+
+// Status word set by kernels whose bounded waits gave up (0 = ok).
+int device_status(int* status, bool reset);
+
+// Error plumbing shared by all host entry points.
+void set_error(const char* fmt, ...);
+const char* last_error();
+
+
+}  // namespace ti

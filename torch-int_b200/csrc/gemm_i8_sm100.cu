@@ -1,0 +1,610 @@
+// W8A8 contraction for sm_100a: C[b] = epilogue(A[b] * B[b]^T), A [M,K] and
+// B [N,K] int8 with K contiguous (both "K-major"), int32 accumulation.
+//
+// One persistent CTA per SM walks a list of 128 x BN output tiles.  Inside a
+// CTA the work is split by warp:
+//   warp 0    TMA producer: cp.async.bulk.tensor loads of a 128 x 128-byte A
+//             tile and a BN x 128-byte B tile into a ring of 128B-swizzled
+//             shared-memory stages, completion counted on "full" mbarriers;
+//   warp 1    MMA issuer: one thread issues tcgen05.mma.kind::i8 (M=128, N=BN,
+//             K=32) over each stage, accumulating in TMEM, and hands stages
+//             back through tcgen05.commit on "empty" mbarriers;
+//   warps 2-5 epilogue: tcgen05.ld the int32 accumulator (one TMEM lane = one
+//             output row per thread), apply the fp32 epilogue and store.
+// TMEM holds two accumulators (2 x BN columns), so the epilogue of tile i runs
+// while the mainloop of tile i+1 fills the other one.
+//
+// Replaces the CUTLASS 2.x device::Gemm / device::GemmBatched instantiations of
+// the reference (torch_int/kernels/linear.cu:34-45,163-172,270-279,393-401,
+// 500-519; torch_int/kernels/bmm.cu:33-41,133-141,233-241).  The bias is read
+// as a length-N vector in the epilogue instead of a materialised M x N matrix
+// (linear.cu:83,420).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <mutex>
+
+#include "gemm_i8.h"
+#include "sm100_ptx.cuh"
+
+namespace ti {
+
+namespace {
+
+constexpr int BM = 128;        // rows of C per tile = TMEM lanes
+constexpr int BK = 128;        // bytes (= int8 elements) of K per stage: one swizzle row
+constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr int SMEM_BUDGET = 227 * 1024;
+
+struct KernelParams {
+  void* C;
+  const void* bias;
+  int M, N, K;
+  int num_kb;               // ceil(K / BK)
+  int m_tiles, n_tiles;     // per batch entry
+  int batch, batch2;
+  long long ldc, strideC, stride2C;
+  long long total_tiles;
+  float alpha, beta;
+  int group_m;              // rasterisation: M tiles per column sweep
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int AUX_BYTES = 2 * BN * 4 + 256;  // bias tiles + barriers
+  static constexpr int STAGES_RAW = (SMEM_BUDGET - 1024 - AUX_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32..256, multiple of 32");
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
+  static_assert(STAGES >= 2, "need at least two stages");
+};
+
+struct TileCoord {
+  int m_tile, n_tile, b1, b2;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(long long t, const KernelParams& p) {
+  const int per_batch = p.m_tiles * p.n_tiles;
+  const long long bidx = t / per_batch;
+  int r = static_cast<int>(t - bidx * per_batch);
+  TileCoord c;
+  c.b1 = static_cast<int>(bidx % p.batch);
+  c.b2 = static_cast<int>(bidx / p.batch);
+  // Grouped order: sweep all N tiles for a band of `group_m` M tiles, so CTAs
+  // that run at the same time share A rows and B rows in L2.
+  const int group_size = p.group_m * p.n_tiles;
+  const int g = r / group_size;
+  const int first_m = g * p.group_m;
+  const int gm = min(p.m_tiles - first_m, p.group_m);
+  r -= g * group_size;
+  c.m_tile = first_m + r % gm;
+  c.n_tile = r / gm;
+  return c;
+}
+
+__device__ __forceinline__ int sat_rne_s8(float y) {
+  int v = __float2int_rn(y);  // cvt.rni.s32.f32: RNE, saturating, NaN -> 0
+  return max(-128, min(127, v));
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  return (static_cast<uint32_t>(a) & 0xFFu) | ((static_cast<uint32_t>(b) & 0xFFu) << 8) |
+         ((static_cast<uint32_t>(c) & 0xFFu) << 16) | ((static_cast<uint32_t>(d) & 0xFFu) << 24);
+}
+
+template <int EPI>
+struct EpiTraits {
+  static constexpr bool kOutS8 =
+      EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU || EPI == EPI_S8_ALPHA;
+  static constexpr bool kHasBias = EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU ||
+                                   EPI == EPI_F32_BIAS_F32 || EPI == EPI_S32_BIAS_S32_ADD ||
+                                   EPI == EPI_S32_BIAS_S32_SCALE;
+  static constexpr int kOutBytes = kOutS8 ? 1 : 4;
+};
+
+// One accumulator value -> one output value (as raw 32 bits; int8 outputs are
+// returned as an int in [-128,127]).  `t` is the bias term prepared per column:
+// beta*float(bias) as float bits for the scaled forms, the raw int32 bias for
+// EPI_S32_BIAS_S32_ADD.
+template <int EPI>
+__device__ __forceinline__ uint32_t epilogue_one(uint32_t acc_bits, uint32_t t, float alpha) {
+  const int acc = static_cast<int>(acc_bits);
+  if constexpr (EPI == EPI_S32_RAW) {
+    return acc_bits;
+  } else if constexpr (EPI == EPI_S32_BIAS_S32_ADD) {
+    return acc_bits + t;  // two's-complement wrap-around
+  } else {
+    const float a = __int2float_rn(acc);
+    float y;
+    if constexpr (EPI == EPI_F32_ALPHA || EPI == EPI_S8_ALPHA)
+      y = alpha * a;
+    else
+      y = __fmaf_rn(alpha, a, __uint_as_float(t));
+    if constexpr (EPI == EPI_S8_BIAS_S8_RELU) y = fmaxf(y, 0.f);
+    if constexpr (EpiTraits<EPI>::kOutS8)
+      return static_cast<uint32_t>(sat_rne_s8(y));
+    else if constexpr (EPI == EPI_S32_BIAS_S32_SCALE)
+      return static_cast<uint32_t>(__float2int_rn(y));
+    else
+      return __float_as_uint(y);
+  }
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const KernelParams p) {
+  using C = Cfg<BN>;
+  using T = EpiTraits<EPI>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* aux = smem + C::STAGES * C::STAGE_BYTES;
+  uint32_t* bias_smem = reinterpret_cast<uint32_t*>(aux);  // [2][BN]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aux + 2 * BN * 4);
+  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* empty_bar = bars + C::STAGES;       // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * C::STAGES;   // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tfull_bar[b]), 1);
+      mbar_init(smem_u32(&tempty_bar[b]), EPI_THREADS / 32);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = decode_tile(t, p);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, TI_ERR_WAIT_EMPTY);
+          if (!ok) break;
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(fb, C::STAGE_BYTES);
+          uint8_t* sa = smem + stage * C::STAGE_BYTES;
+          tma_load_4d(smem_u32(sa), &tmap_a, fb, kb * BK, tc.m_tile * BM, tc.b1, tc.b2);
+          tma_load_4d(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, tc.n_tile * BN, tc.b1, tc.b2);
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_s8s8s32(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        ok = mbar_wait(smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1, abort_flag,
+                       TI_ERR_WAIT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, TI_ERR_WAIT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint64_t da = make_smem_desc_sw128(sa);
+          const uint64_t db = make_smem_desc_sw128(sa + C::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // +32 bytes of K inside the 128-byte swizzle row = +2 in the
+            // (address >> 4) field of the descriptor.
+            umma_i8<1>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(smem_u32(&tfull_bar[buf]));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    const int et = threadIdx.x - 64;
+    int it = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+      const TileCoord tc = decode_tile(t, p);
+      const int buf = it & 1;
+      const int n0 = tc.n_tile * BN;
+      if constexpr (T::kHasBias) {
+        uint32_t* bs = bias_smem + buf * BN;
+        for (int j = et; j < BN; j += EPI_THREADS) {
+          const int n = n0 + j;
+          uint32_t v = 0;
+          if (n < p.N) {
+            if constexpr (EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU)
+              v = __float_as_uint(p.beta * static_cast<float>(static_cast<const int8_t*>(p.bias)[n]));
+            else if constexpr (EPI == EPI_F32_BIAS_F32)
+              v = __float_as_uint(p.beta * static_cast<const float*>(p.bias)[n]);
+            else if constexpr (EPI == EPI_S32_BIAS_S32_SCALE)
+              v = __float_as_uint(p.beta *
+                                  __int2float_rn(static_cast<const int32_t*>(p.bias)[n]));
+            else
+              v = static_cast<uint32_t>(static_cast<const int32_t*>(p.bias)[n]);
+          }
+          bs[j] = v;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+      }
+      ok = mbar_wait(smem_u32(&tfull_bar[buf]), (it >> 1) & 1, abort_flag, TI_ERR_WAIT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+
+      const int row = tc.m_tile * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      uint8_t* crow = static_cast<uint8_t*>(p.C) +
+                      (static_cast<long long>(tc.b2) * p.stride2C +
+                       static_cast<long long>(tc.b1) * p.strideC +
+                       static_cast<long long>(row) * p.ldc + n0) *
+                          T::kOutBytes;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const uint32_t* bs = bias_smem + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (n0 + c * 32 >= p.N) break;  // uniform over the CTA
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 tb = make_uint4(0, 0, 0, 0);
+            if constexpr (T::kHasBias) tb = reinterpret_cast<const uint4*>(bs)[c * 8 + q];
+            v[q * 4 + 0] = epilogue_one<EPI>(v[q * 4 + 0], tb.x, p.alpha);
+            v[q * 4 + 1] = epilogue_one<EPI>(v[q * 4 + 1], tb.y, p.alpha);
+            v[q * 4 + 2] = epilogue_one<EPI>(v[q * 4 + 2], tb.z, p.alpha);
+            v[q * 4 + 3] = epilogue_one<EPI>(v[q * 4 + 3], tb.w, p.alpha);
+          }
+          if constexpr (T::kOutS8) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (n0 + c * 32 + h * 16 < p.N) {
+                uint4 o;
+                o.x = pack4(v[h * 16 + 0], v[h * 16 + 1], v[h * 16 + 2], v[h * 16 + 3]);
+                o.y = pack4(v[h * 16 + 4], v[h * 16 + 5], v[h * 16 + 6], v[h * 16 + 7]);
+                o.z = pack4(v[h * 16 + 8], v[h * 16 + 9], v[h * 16 + 10], v[h * 16 + 11]);
+                o.w = pack4(v[h * 16 + 12], v[h * 16 + 13], v[h * 16 + 14], v[h * 16 + 15]);
+                *reinterpret_cast<uint4*>(crow + c * 32 + h * 16) = o;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              if (n0 + c * 32 + q * 4 < p.N) {
+                uint4 o = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                *reinterpret_cast<uint4*>(crow + (c * 32 + q * 4) * 4) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[buf]));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up: give copies and MMAs that may still be in flight a bounded
+    // grace period before shared memory and TMEM are released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// K-major int8 operand [batch2, batch, rows, K] -> 4-D tensor map with a
+// (128 bytes of K) x box_rows x 1 x 1 box, 128-byte swizzle, zero fill.
+bool make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t K, int64_t rows, int64_t batch,
+                      int64_t batch2, int64_t ld, int64_t stride, int64_t stride2, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return false;
+  }
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(batch), static_cast<cuuint64_t>(batch2)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(stride),
+                           static_cast<cuuint64_t>(stride2)};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (CUresult %d) for K=%lld rows=%lld batch=%lld x %lld "
+              "ld=%lld stride=%lld stride2=%lld",
+              static_cast<int>(r), (long long)K, (long long)rows, (long long)batch,
+              (long long)batch2, (long long)ld, (long long)stride, (long long)stride2);
+    return false;
+  }
+  return true;
+}
+
+int num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
+  }
+  return cached[dev];
+}
+
+template <int BN, int EPI>
+int launch_one(const GemmProblem& g, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+      return TI_E_CUDA;
+    }
+    attr_done[dev] = true;
+  }
+  CUtensorMap ta, tb;
+  if (!make_operand_map(&ta, g.A, g.K, g.M, g.batch, g.batch2, g.lda, g.strideA, g.stride2A, BM))
+    return TI_E_CUDA;
+  if (!make_operand_map(&tb, g.B, g.K, g.N, g.batch, g.batch2, g.ldb, g.strideB, g.stride2B, BN))
+    return TI_E_CUDA;
+  KernelParams p;
+  p.C = g.C;
+  p.bias = g.bias;
+  p.M = static_cast<int>(g.M);
+  p.N = static_cast<int>(g.N);
+  p.K = static_cast<int>(g.K);
+  p.num_kb = static_cast<int>((g.K + BK - 1) / BK);
+  p.m_tiles = static_cast<int>((g.M + BM - 1) / BM);
+  p.n_tiles = static_cast<int>((g.N + BN - 1) / BN);
+  p.batch = static_cast<int>(g.batch);
+  p.batch2 = static_cast<int>(g.batch2);
+  p.ldc = g.ldc;
+  p.strideC = g.strideC;
+  p.stride2C = g.stride2C;
+  p.total_tiles = static_cast<long long>(p.m_tiles) * p.n_tiles * g.batch * g.batch2;
+  p.alpha = g.alpha;
+  p.beta = g.beta;
+  p.group_m = 16;
+  const int sms = num_sms();
+  const int grid = static_cast<int>(p.total_tiles < sms ? p.total_tiles : sms);
+  gemm_i8_kernel<BN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("gemm_i8_kernel<%d,%d> launch failed: %s", BN, EPI, cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  return TI_OK;
+}
+
+template <int EPI>
+int launch_bn(const GemmProblem& g, int bn, cudaStream_t stream) {
+  switch (bn) {
+    case 256: return launch_one<256, EPI>(g, stream);
+    case 128: return launch_one<128, EPI>(g, stream);
+    case 64: return launch_one<64, EPI>(g, stream);
+    case 32: return launch_one<32, EPI>(g, stream);
+  }
+  set_error("unsupported N tile %d", bn);
+  return TI_E_INVALID;
+}
+
+// Pick the N tile: the cost of a configuration is (waves over the SMs) x (time
+// of one k-block of that tile shape).  A k-block is four M=128 MMAs, each
+// bound either by the tensor pipe (N/2 cycles) or by reading A (4 KB) and B
+// (32*N bytes) from shared memory at 128 B/cycle.
+int choose_bn(const GemmProblem& g) {
+  const int cands[4] = {256, 128, 64, 32};
+  const int sms = num_sms();
+  const long long m_tiles = (g.M + BM - 1) / BM;
+  double best = 1e300;
+  int best_bn = 256;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cands[i];
+    if (bn > 32 && bn / 2 >= g.N) continue;  // tile mostly padding
+    const long long tiles = m_tiles * ((g.N + bn - 1) / bn) * g.batch * g.batch2;
+    const long long waves = (tiles + sms - 1) / sms;
+    const double mma = bn / 2.0;
+    const double smem = (4096.0 + 32.0 * bn) / 128.0;
+    const double cost = static_cast<double>(waves) * (mma > smem ? mma : smem);
+    if (cost < best * 0.999) {
+      best = cost;
+      best_bn = bn;
+    }
+  }
+  return best_bn;
+}
+
+}  // namespace
+
+int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
+  if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0 || g.batch2 < 0) {
+    set_error("negative dimension");
+    return TI_E_INVALID;
+  }
+  if (g.M == 0 || g.N == 0 || g.batch == 0 || g.batch2 == 0) return TI_OK;  // empty output
+  if (g.K == 0) {
+    set_error("K must be positive");
+    return TI_E_INVALID;
+  }
+  if (!g.A || !g.B || !g.C) {
+    set_error("null operand pointer");
+    return TI_E_INVALID;
+  }
+  const bool out_s8 = g.epilogue == EPI_S8_BIAS_S8 || g.epilogue == EPI_S8_BIAS_S8_RELU ||
+                      g.epilogue == EPI_S8_ALPHA;
+  const bool has_bias = g.epilogue == EPI_S8_BIAS_S8 || g.epilogue == EPI_S8_BIAS_S8_RELU ||
+                        g.epilogue == EPI_F32_BIAS_F32 || g.epilogue == EPI_S32_BIAS_S32_ADD ||
+                        g.epilogue == EPI_S32_BIAS_S32_SCALE;
+  if (has_bias && !g.bias) {
+    set_error("this epilogue needs a bias vector");
+    return TI_E_INVALID;
+  }
+  // The shape rules of the reference kernels (128-bit vector accesses): K a
+  // multiple of 16, N a multiple of 16 for int8 outputs and of 4 for 32-bit
+  // outputs.  They are also what TMA (16-byte strides) and the 16-byte stores
+  // of the epilogue need.
+  if (g.K % 16 != 0) {
+    set_error("K=%lld must be a multiple of 16", (long long)g.K);
+    return TI_E_INVALID;
+  }
+  const int nmult = out_s8 ? 16 : 4;
+  if (g.N % nmult != 0) {
+    set_error("N=%lld must be a multiple of %d for this output type", (long long)g.N, nmult);
+    return TI_E_INVALID;
+  }
+  if (g.lda % 16 || g.ldb % 16 || g.strideA % 16 || g.strideB % 16 || g.stride2A % 16 ||
+      g.stride2B % 16 || g.lda < g.K || g.ldb < g.K) {
+    set_error("operand strides must be multiples of 16 elements and >= K");
+    return TI_E_INVALID;
+  }
+  if (g.ldc % nmult || g.strideC % nmult || g.stride2C % nmult || g.ldc < g.N) {
+    set_error("output strides must be multiples of %d elements and ldc >= N", nmult);
+    return TI_E_INVALID;
+  }
+  if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) |
+       reinterpret_cast<uintptr_t>(g.C)) & 15) {
+    set_error("operand and output pointers must be 16-byte aligned");
+    return TI_E_INVALID;
+  }
+  if (g.M > 0x7FFFFFFF - 256 || g.N > 0x7FFFFFFF - 256 || g.K > 0x7FFFFFFF - 256 ||
+      g.batch > 0x7FFFFFFF || g.batch2 > 0x7FFFFFFF) {
+    set_error("dimension too large");
+    return TI_E_INVALID;
+  }
+  int bn = g.force_bn ? g.force_bn : choose_bn(g);
+  switch (g.epilogue) {
+    case EPI_S8_BIAS_S8: return launch_bn<EPI_S8_BIAS_S8>(g, bn, stream);
+    case EPI_S8_BIAS_S8_RELU: return launch_bn<EPI_S8_BIAS_S8_RELU>(g, bn, stream);
+    case EPI_F32_BIAS_F32: return launch_bn<EPI_F32_BIAS_F32>(g, bn, stream);
+    case EPI_S32_BIAS_S32_ADD: return launch_bn<EPI_S32_BIAS_S32_ADD>(g, bn, stream);
+    case EPI_S32_BIAS_S32_SCALE: return launch_bn<EPI_S32_BIAS_S32_SCALE>(g, bn, stream);
+    case EPI_F32_ALPHA: return launch_bn<EPI_F32_ALPHA>(g, bn, stream);
+    case EPI_S8_ALPHA: return launch_bn<EPI_S8_ALPHA>(g, bn, stream);
+    case EPI_S32_RAW: return launch_bn<EPI_S32_RAW>(g, bn, stream);
+  }
+  set_error("unknown epilogue %d", g.epilogue);
+  return TI_E_INVALID;
+}
+
+// Reads (and optionally clears) the status word the kernels of this file set
+// when a bounded wait gives up.  Synchronises the device.
+int device_status(int* status, bool reset) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    set_error("cudaDeviceSynchronize failed: %s", cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  int v = 0;
+  e = cudaMemcpyFromSymbol(&v, ti_kernel_status, sizeof(int));
+  if (e != cudaSuccess) {
+    set_error("cudaMemcpyFromSymbol failed: %s", cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  if (reset && v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(ti_kernel_status, &zero, sizeof(int));
+  }
+  *status = v;
+  return TI_OK;
+}
+
+// ------------------------------------------------------------ error plumbing
+namespace {
+thread_local char g_err[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+const char* last_error() { return g_err; }
+
+}  // namespace ti

@@ -1,0 +1,487 @@
+// Bandwidth-bound row kernels of the W8A8 path:
+//   layernorm_q         q = int8(clamp(rne(LN(x) * gamma + beta), -128, 127))
+//                       (reference: torch_int/nn/fused.py:13-18, four ATen launches)
+//   dq_add_layernorm_q  r = residual + scale * int32_in (+ bias); q as above from r
+//                       (reference: torch_int/kernels/fused.cu:17-23, five ATen launches)
+//   softmax_q           p = int8(rne(127 * softmax(max(s + mask, FLT_LOWEST))))
+//                       (reference: torch_int/models/opt.py:139-178)
+// One CTA owns one row.  The row is read once with 128-bit loads, kept in
+// registers for the two reductions (warp shuffles + one shared-memory step) and
+// written once, so HBM traffic equals the algorithmic bytes.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "gemm_i8.h"
+#include "norm_quant.h"
+
+namespace ti {
+namespace {
+
+constexpr int kMaxVpt = 16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide reduction; every thread gets the result.  `scratch` holds one
+// float per warp and may be reused right after the call returns.
+template <int THREADS, bool kMax>
+__device__ __forceinline__ float block_reduce(float v, float* scratch) {
+  constexpr int W = THREADS / 32;
+  v = kMax ? warp_max(v) : warp_sum(v);
+  if constexpr (W == 1) return v;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // scratch may still be read from the previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < W ? scratch[lane] : (kMax ? -FLT_MAX : 0.f);
+  return kMax ? warp_max(r) : warp_sum(r);
+}
+
+__device__ __forceinline__ int quant_s8(float y) {
+  // clamp to [-128,127] then round half to even == RNE then saturate
+  int v = __float2int_rn(y);
+  return max(-128, min(127, v));
+}
+
+__device__ __forceinline__ uint32_t pack_s8x4(float a, float b, float c, float d) {
+  return (static_cast<uint32_t>(quant_s8(a)) & 0xFFu) | ((static_cast<uint32_t>(quant_s8(b)) & 0xFFu) << 8) |
+         ((static_cast<uint32_t>(quant_s8(c)) & 0xFFu) << 16) |
+         ((static_cast<uint32_t>(quant_s8(d)) & 0xFFu) << 24);
+}
+
+template <typename T>
+__device__ __forceinline__ float4 load4(const T* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4<__half>(const __half* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __half2 a = *reinterpret_cast<const __half2*>(&u.x);
+  const __half2 b = *reinterpret_cast<const __half2*>(&u.y);
+  const float2 fa = __half22float2(a), fb = __half22float2(b);
+  return make_float4(fa.x, fa.y, fb.x, fb.y);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float4 v) {
+  *reinterpret_cast<float4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void store4<__half>(__half* p, float4 v) {
+  const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&a);
+  u.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// With a 16-bit residual stream the reference rounds every intermediate tensor
+// to fp16 (the LayerNorm output is an fp16 tensor before clamp/round).
+template <typename T>
+__device__ __forceinline__ float round_to_storage(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ float round_to_storage<__half>(float v) {
+  return __half2float(__float2half_rn(v));
+}
+
+// Shared tail: LayerNorm statistics over the register-resident row `x`,
+// affine transform, quantisation, 4-byte stores.
+template <typename T, int THREADS, int VPT>
+__device__ __forceinline__ void layernorm_quant_row(float4 (&x)[VPT], int h4, const float* gamma,
+                                                    const float* beta, float eps, int H,
+                                                    int8_t* qrow, float* scratch) {
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) s += (x[j].x + x[j].y) + (x[j].z + x[j].w);
+  }
+  const float mean = block_reduce<THREADS, false>(s, scratch) / static_cast<float>(H);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) {
+      const float a = x[j].x - mean, b = x[j].y - mean, c = x[j].z - mean, d = x[j].w - mean;
+      ss += (a * a + b * b) + (c * c + d * d);
+    }
+  }
+  const float var = block_reduce<THREADS, false>(ss, scratch) / static_cast<float>(H);
+  const float rstd = __fdiv_rn(1.f, __fsqrt_rn(var + eps));
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) {
+      const float4 g = *reinterpret_cast<const float4*>(gamma + 4 * i);
+      const float4 b = *reinterpret_cast<const float4*>(beta + 4 * i);
+      const float y0 = round_to_storage<T>(__fmaf_rn((x[j].x - mean) * rstd, g.x, b.x));
+      const float y1 = round_to_storage<T>(__fmaf_rn((x[j].y - mean) * rstd, g.y, b.y));
+      const float y2 = round_to_storage<T>(__fmaf_rn((x[j].z - mean) * rstd, g.z, b.z));
+      const float y3 = round_to_storage<T>(__fmaf_rn((x[j].w - mean) * rstd, g.w, b.w));
+      *reinterpret_cast<uint32_t*>(qrow + 4 * i) = pack_s8x4(y0, y1, y2, y3);
+    }
+  }
+}
+
+template <typename T, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+layernorm_q_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
+                   const float* __restrict__ beta, float eps, int8_t* __restrict__ q, int H,
+                   long long ldx, long long ldq) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const int h4 = H >> 2;
+  const T* xr = x + row * ldx;
+  float4 v[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) v[j] = load4<T>(xr + 4 * i);
+  }
+  layernorm_quant_row<T, THREADS, VPT>(v, h4, gamma, beta, eps, H, q + row * ldq, scratch);
+}
+
+template <typename T, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+dq_add_layernorm_q_kernel(const int32_t* __restrict__ in, float scale, const T* __restrict__ res,
+                          const float* __restrict__ in_bias, const float* __restrict__ gamma,
+                          const float* __restrict__ beta, float eps, T* __restrict__ res_out,
+                          int8_t* __restrict__ q, int H) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const int h4 = H >> 2;
+  const int32_t* ir = in + row * H;
+  const T* rr = res + row * H;
+  T* ro = res_out + row * H;
+  float4 v[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) {
+      const int4 a = *reinterpret_cast<const int4*>(ir + 4 * i);
+      const float4 r = load4<T>(rr + 4 * i);
+      float4 f = make_float4(round_to_storage<T>(__int2float_rn(a.x)), round_to_storage<T>(__int2float_rn(a.y)),
+                             round_to_storage<T>(__int2float_rn(a.z)), round_to_storage<T>(__int2float_rn(a.w)));
+      float4 o;
+      if (in_bias != nullptr) {
+        // Extension for the row-parallel tensor-parallel path: the int32 input is
+        // an all-reduced accumulator, so the linear layer's fp32 bias is applied
+        // here: d = fma(scale, acc, bias) as the fp32-output linear does, then
+        // the residual add.
+        const float4 bb = *reinterpret_cast<const float4*>(in_bias + 4 * i);
+        o.x = r.x + __fmaf_rn(scale, f.x, bb.x);
+        o.y = r.y + __fmaf_rn(scale, f.y, bb.y);
+        o.z = r.z + __fmaf_rn(scale, f.z, bb.z);
+        o.w = r.w + __fmaf_rn(scale, f.w, bb.w);
+      } else {
+        o.x = __fmaf_rn(scale, f.x, r.x);
+        o.y = __fmaf_rn(scale, f.y, r.y);
+        o.z = __fmaf_rn(scale, f.z, r.z);
+        o.w = __fmaf_rn(scale, f.w, r.w);
+      }
+      o.x = round_to_storage<T>(o.x);
+      o.y = round_to_storage<T>(o.y);
+      o.z = round_to_storage<T>(o.z);
+      o.w = round_to_storage<T>(o.w);
+      store4<T>(ro + 4 * i, o);
+      v[j] = o;
+    }
+  }
+  layernorm_quant_row<T, THREADS, VPT>(v, h4, gamma, beta, eps, H, q + row * static_cast<long long>(H),
+                                       scratch);
+}
+
+// Scalar, multi-pass fallback for row lengths the register-resident kernels do
+// not cover (H not a multiple of 4, or H > 256 * 4 * kMaxVpt).  Rows are read
+// three times; the second and third reads hit L1/L2.
+template <typename T, bool kDq>
+__global__ void __launch_bounds__(256)
+layernorm_q_generic_kernel(const T* __restrict__ x, const int32_t* __restrict__ in, float scale,
+                           const float* __restrict__ in_bias, const float* __restrict__ gamma,
+                           const float* __restrict__ beta, float eps, T* __restrict__ res_out,
+                           int8_t* __restrict__ q, int H, long long ldx, long long ldq) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * ldx;
+  auto value = [&](int i) -> float {
+    float r = static_cast<float>(xr[i]);
+    if constexpr (kDq) {
+      const float f = round_to_storage<T>(__int2float_rn(in[row * H + i]));
+      if (in_bias != nullptr)
+        r = r + __fmaf_rn(scale, f, in_bias[i]);
+      else
+        r = __fmaf_rn(scale, f, r);
+      r = round_to_storage<T>(r);
+    }
+    return r;
+  };
+  float s = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float v = value(i);
+    if constexpr (kDq) res_out[row * H + i] = static_cast<T>(v);
+    s += v;
+  }
+  const float mean = block_reduce<256, false>(s, scratch) / static_cast<float>(H);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float d = value(i) - mean;
+    ss += d * d;
+  }
+  const float var = block_reduce<256, false>(ss, scratch) / static_cast<float>(H);
+  const float rstd = __fdiv_rn(1.f, __fsqrt_rn(var + eps));
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float y = round_to_storage<T>(__fmaf_rn((value(i) - mean) * rstd, gamma[i], beta[i]));
+    q[row * ldq + i] = static_cast<int8_t>(quant_s8(y));
+  }
+}
+
+// Row softmax of fp32 scores -> int8 probabilities in [0,127].
+//   s = score + mask (additive, optional);  s = max(s, -FLT_MAX);  p = softmax(s)
+//   out = int8(rne(127 * p))
+// `causal` >= 0 generates the additive mask instead of reading one: column j of
+// row t (t counted inside its [T,S] matrix) is kept iff j <= t + causal, every
+// other column gets -FLT_MAX, which is what the reference's mask tensor holds.
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+softmax_q_kernel(const float* __restrict__ scores, const float* __restrict__ mask,
+                 int8_t* __restrict__ out, int T, int S, int heads, long long lds, long long ldo,
+                 int causal) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;        // over batch*heads*T
+  const int t = static_cast<int>(row % T);
+  const long long bh = row / T;
+  const float* sr = scores + row * lds;
+  const float* mr = mask ? mask + ((bh / heads) * T + t) * static_cast<long long>(S) : nullptr;
+  const int s4 = S >> 2;
+  float4 v[VPT];
+  float mx = -FLT_MAX;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < s4) {
+      float4 a = *reinterpret_cast<const float4*>(sr + 4 * i);
+      if (mr) {
+        const float4 m = *reinterpret_cast<const float4*>(mr + 4 * i);
+        a.x += m.x; a.y += m.y; a.z += m.z; a.w += m.w;
+      } else if (causal >= 0) {
+        const int lim = t + causal;
+        if (4 * i + 0 > lim) a.x += -FLT_MAX;
+        if (4 * i + 1 > lim) a.y += -FLT_MAX;
+        if (4 * i + 2 > lim) a.z += -FLT_MAX;
+        if (4 * i + 3 > lim) a.w += -FLT_MAX;
+      }
+      a.x = fmaxf(a.x, -FLT_MAX); a.y = fmaxf(a.y, -FLT_MAX);
+      a.z = fmaxf(a.z, -FLT_MAX); a.w = fmaxf(a.w, -FLT_MAX);
+      v[j] = a;
+      mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+    }
+  }
+  mx = block_reduce<THREADS, true>(mx, scratch);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < s4) {
+      v[j].x = expf(v[j].x - mx); v[j].y = expf(v[j].y - mx);
+      v[j].z = expf(v[j].z - mx); v[j].w = expf(v[j].w - mx);
+      sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+  }
+  sum = block_reduce<THREADS, false>(sum, scratch);
+  int8_t* orow = out + row * ldo;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < s4) {
+      // softmax = exp / sum (a true division, as torch does), then * 127, RNE.
+      const float p0 = __fdiv_rn(v[j].x, sum) * 127.f, p1 = __fdiv_rn(v[j].y, sum) * 127.f;
+      const float p2 = __fdiv_rn(v[j].z, sum) * 127.f, p3 = __fdiv_rn(v[j].w, sum) * 127.f;
+      *reinterpret_cast<uint32_t*>(orow + 4 * i) = pack_s8x4(p0, p1, p2, p3);
+    }
+  }
+}
+
+template <typename F>
+int check_launch(const char* name, F&& f) {
+  f();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s launch failed: %s", name, cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  return TI_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+#define TI_VPT_SWITCH(vpt, ...)                                       \
+  switch (vpt) {                                                      \
+    case 1: { constexpr int VPT = 1; __VA_ARGS__; break; }            \
+    case 2: { constexpr int VPT = 2; __VA_ARGS__; break; }            \
+    case 3: { constexpr int VPT = 3; __VA_ARGS__; break; }            \
+    case 4: { constexpr int VPT = 4; __VA_ARGS__; break; }            \
+    case 5: { constexpr int VPT = 5; __VA_ARGS__; break; }            \
+    case 6: { constexpr int VPT = 6; __VA_ARGS__; break; }            \
+    case 7: { constexpr int VPT = 7; __VA_ARGS__; break; }            \
+    case 8: { constexpr int VPT = 8; __VA_ARGS__; break; }            \
+    case 9: case 10: { constexpr int VPT = 10; __VA_ARGS__; break; }  \
+    case 11: case 12: { constexpr int VPT = 12; __VA_ARGS__; break; } \
+    case 13: case 14: { constexpr int VPT = 14; __VA_ARGS__; break; } \
+    default: { constexpr int VPT = 16; __VA_ARGS__; break; }          \
+  }
+
+template <typename T>
+int layernorm_q_typed(const T* x, const float* gamma, const float* beta, float eps, int8_t* q,
+                      int64_t rows, int64_t H, cudaStream_t stream) {
+  const int h4 = static_cast<int>(H / 4);
+  const bool fast = H % 4 == 0 && h4 <= 256 * kMaxVpt && aligned16(x) && aligned16(gamma) &&
+                    aligned16(beta) && (reinterpret_cast<uintptr_t>(q) & 3) == 0;
+  const unsigned grid = static_cast<unsigned>(rows);
+  if (!fast)
+    return check_launch("layernorm_q_generic", [&] {
+      layernorm_q_generic_kernel<T, false><<<grid, 256, 0, stream>>>(
+          x, nullptr, 0.f, nullptr, gamma, beta, eps, nullptr, q, static_cast<int>(H), H, H);
+    });
+  if (h4 <= 128)
+    return check_launch("layernorm_q", [&] {
+      layernorm_q_kernel<T, 128, 1><<<grid, 128, 0, stream>>>(x, gamma, beta, eps, q,
+                                                              static_cast<int>(H), H, H);
+    });
+  const int vpt = (h4 + 255) / 256;
+  int rc = TI_OK;
+  TI_VPT_SWITCH(vpt, rc = check_launch("layernorm_q", [&] {
+                  layernorm_q_kernel<T, 256, VPT><<<grid, 256, 0, stream>>>(
+                      x, gamma, beta, eps, q, static_cast<int>(H), H, H);
+                }));
+  return rc;
+}
+
+template <typename T>
+int dq_add_layernorm_q_typed(const int32_t* in, float scale, const T* res, const float* in_bias,
+                             const float* gamma, const float* beta, float eps, T* res_out,
+                             int8_t* q, int64_t rows, int64_t H, cudaStream_t stream) {
+  const int h4 = static_cast<int>(H / 4);
+  const bool fast = H % 4 == 0 && h4 <= 256 * kMaxVpt && aligned16(in) && aligned16(res) &&
+                    aligned16(res_out) && aligned16(gamma) && aligned16(beta) &&
+                    (in_bias == nullptr || aligned16(in_bias)) &&
+                    (reinterpret_cast<uintptr_t>(q) & 3) == 0;
+  const unsigned grid = static_cast<unsigned>(rows);
+  if (!fast)
+    return check_launch("dq_add_layernorm_q_generic", [&] {
+      layernorm_q_generic_kernel<T, true><<<grid, 256, 0, stream>>>(
+          res, in, scale, in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H), H, H);
+    });
+  if (h4 <= 128)
+    return check_launch("dq_add_layernorm_q", [&] {
+      dq_add_layernorm_q_kernel<T, 128, 1><<<grid, 128, 0, stream>>>(
+          in, scale, res, in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H));
+    });
+  const int vpt = (h4 + 255) / 256;
+  int rc = TI_OK;
+  TI_VPT_SWITCH(vpt, rc = check_launch("dq_add_layernorm_q", [&] {
+                  dq_add_layernorm_q_kernel<T, 256, VPT><<<grid, 256, 0, stream>>>(
+                      in, scale, res, in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H));
+                }));
+  return rc;
+}
+
+}  // namespace
+
+int layernorm_q(const void* x, int x_is_half, const float* gamma, const float* beta, float eps,
+                int8_t* q, int64_t rows, int64_t H, cudaStream_t stream) {
+  if (rows < 0 || H <= 0) {
+    set_error("layernorm_q: bad shape rows=%lld H=%lld", (long long)rows, (long long)H);
+    return TI_E_INVALID;
+  }
+  if (rows == 0) return TI_OK;
+  if (!x || !gamma || !beta || !q) {
+    set_error("layernorm_q: null pointer");
+    return TI_E_INVALID;
+  }
+  if (rows > 0x7FFFFFFF) {
+    set_error("layernorm_q: too many rows");
+    return TI_E_INVALID;
+  }
+  if (x_is_half)
+    return layernorm_q_typed<__half>(static_cast<const __half*>(x), gamma, beta, eps, q, rows, H, stream);
+  return layernorm_q_typed<float>(static_cast<const float*>(x), gamma, beta, eps, q, rows, H, stream);
+}
+
+int dq_add_layernorm_q(const int32_t* in, float scale, const void* res, int res_is_half,
+                       const float* in_bias, const float* gamma, const float* beta, float eps,
+                       void* res_out, int8_t* q, int64_t rows, int64_t H, cudaStream_t stream) {
+  if (rows < 0 || H <= 0) {
+    set_error("dq_add_layernorm_q: bad shape rows=%lld H=%lld", (long long)rows, (long long)H);
+    return TI_E_INVALID;
+  }
+  if (rows == 0) return TI_OK;
+  if (!in || !res || !gamma || !beta || !res_out || !q) {
+    set_error("dq_add_layernorm_q: null pointer");
+    return TI_E_INVALID;
+  }
+  if (rows > 0x7FFFFFFF) {
+    set_error("dq_add_layernorm_q: too many rows");
+    return TI_E_INVALID;
+  }
+  if (res_is_half)
+    return dq_add_layernorm_q_typed<__half>(in, scale, static_cast<const __half*>(res), in_bias, gamma,
+                                            beta, eps, static_cast<__half*>(res_out), q, rows, H, stream);
+  return dq_add_layernorm_q_typed<float>(in, scale, static_cast<const float*>(res), in_bias, gamma,
+                                         beta, eps, static_cast<float*>(res_out), q, rows, H, stream);
+}
+
+int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch_heads, int64_t heads,
+              int64_t T, int64_t S, int64_t lds, int64_t ldo, int causal, cudaStream_t stream) {
+  if (batch_heads < 0 || T < 0 || S <= 0 || heads <= 0) {
+    set_error("softmax_q: bad shape");
+    return TI_E_INVALID;
+  }
+  const int64_t rows = batch_heads * T;
+  if (rows == 0) return TI_OK;
+  if (!scores || !out) {
+    set_error("softmax_q: null pointer");
+    return TI_E_INVALID;
+  }
+  if (S % 4 != 0 || lds % 4 != 0 || ldo % 4 != 0 || !aligned16(scores) || (mask && !aligned16(mask)) ||
+      (reinterpret_cast<uintptr_t>(out) & 3) != 0) {
+    set_error("softmax_q: S and the row strides must be multiples of 4 and pointers 16-byte aligned");
+    return TI_E_INVALID;
+  }
+  const int s4 = static_cast<int>(S / 4);
+  if (s4 > 256 * kMaxVpt || rows > 0x7FFFFFFF) {
+    set_error("softmax_q: S=%lld exceeds the supported maximum of %d", (long long)S, 256 * kMaxVpt * 4);
+    return TI_E_INVALID;
+  }
+  const unsigned grid = static_cast<unsigned>(rows);
+  if (s4 <= 128)
+    return check_launch("softmax_q", [&] {
+      softmax_q_kernel<128, 1><<<grid, 128, 0, stream>>>(scores, mask, out, static_cast<int>(T),
+                                                         static_cast<int>(S), static_cast<int>(heads),
+                                                         lds, ldo, causal);
+    });
+  const int vpt = (s4 + 255) / 256;
+  int rc = TI_OK;
+  TI_VPT_SWITCH(vpt, rc = check_launch("softmax_q", [&] {
+                  softmax_q_kernel<256, VPT><<<grid, 256, 0, stream>>>(
+                      scores, mask, out, static_cast<int>(T), static_cast<int>(S),
+                      static_cast<int>(heads), lds, ldo, causal);
+                }));
+  return rc;
+}
+
+}  // namespace ti

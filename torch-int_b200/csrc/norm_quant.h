@@ -1,0 +1,24 @@
+// Host launchers of the bandwidth-bound row kernels (LayerNorm-quantise,
+// dequant-add-LayerNorm-quantise, softmax-quantise).  All return 0 or a
+// negative TI_E_* code with the message in last_error().
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ti {
+
+int layernorm_q(const void* x, int x_is_half, const float* gamma, const float* beta, float eps,
+                int8_t* q, int64_t rows, int64_t H, cudaStream_t stream);
+
+// `in_bias` (fp32, H elements) is optional; see the kernel for its meaning.
+int dq_add_layernorm_q(const int32_t* in, float scale, const void* res, int res_is_half,
+                       const float* in_bias, const float* gamma, const float* beta, float eps,
+                       void* res_out, int8_t* q, int64_t rows, int64_t H, cudaStream_t stream);
+
+// scores [batch_heads, T, S] fp32 (row stride lds), optional additive mask
+// [batch_heads / heads, T, S] fp32, out int8 [batch_heads, T, S] (row stride
+// ldo).  causal < 0: no generated mask.
+int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch_heads, int64_t heads,
+              int64_t T, int64_t S, int64_t lds, int64_t ldo, int causal, cudaStream_t stream);
+
+}  // namespace ti

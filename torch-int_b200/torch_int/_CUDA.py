@@ -1,0 +1,401 @@
+"""Drop-in for the reference's native extension module ``torch_int._CUDA``.
+
+Exports the nine callables of the reference's pybind11 module with the same
+names, positional arguments and return values
+(torch_int/kernels/bindings.cpp:5-20), implemented by the sm_100a kernels of
+``libtorch_int_b200.so`` through its C ABI (include/torch_int_b200.h).  This
+shim only validates tensors, allocates the output, looks up the device and the
+current stream and forwards raw pointers; it never computes anything itself
+and there is no CPU or PyTorch fallback: importing it without the built
+library, or calling an op with a CPU tensor, raises.
+
+Differences from the reference wrappers, all deliberate:
+  * inputs are validated (dtype, device, contiguity, shape agreement) and a
+    ``RuntimeError`` is raised where the reference would silently compute on
+    assumed-packed strides (torch_int/kernels/linear.cu:429-434);
+  * kernels run on the current stream of the input's device instead of the
+    legacy default stream of the current device;
+  * the bias is read as a vector, no M x N matrix is materialised
+    (torch_int/kernels/linear.cu:83,420).
+Extra callables (not in the reference) are listed at the end of ``__all__``.
+"""
+import ctypes
+import os
+
+import torch
+
+__all__ = [
+    "linear_a8_w8_b8_o8", "linear_relu_a8_w8_b8_o8", "linear_a8_w8_bfp32_ofp32",
+    "linear_a8_w8_b32_o32", "linear_a8_w8_b32_o32_with_scaling",
+    "bmm_s8t_s8n_s8t", "bmm_s8t_s8n_f32t", "bmm_s8t_s8n_s32t", "dq_add_layernorm_q",
+    # extras
+    "layernorm_q", "softmax_q", "dq_add_layernorm_q_bias", "gemm_i8_ex", "device_status",
+    "library_path",
+]
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libtorch_int_b200.so")
+
+
+def library_path():
+    """Path of the shared library this module forwards to."""
+    return _LIB_PATH
+
+
+if not os.path.exists(_LIB_PATH):
+    raise ImportError(
+        f"torch_int._CUDA: {_LIB_PATH} is missing; build it with "
+        "`python torch-int_b200/csrc/build.py` (needs nvcc with sm_100a support). "
+        "There is no fallback implementation.")
+
+_lib = ctypes.CDLL(_LIB_PATH)
+
+_i64, _f32, _i32, _ptr = ctypes.c_int64, ctypes.c_float, ctypes.c_int, ctypes.c_void_p
+
+
+class _GemmDesc(ctypes.Structure):
+    # struct ti_gemm_desc (include/torch_int_b200.h)
+    _fields_ = [
+        ("A", _ptr), ("B", _ptr), ("C", _ptr), ("bias", _ptr),
+        ("M", _i64), ("N", _i64), ("K", _i64),
+        ("batch", _i64), ("batch2", _i64),
+        ("lda", _i64), ("ldb", _i64), ("ldc", _i64),
+        ("strideA", _i64), ("strideB", _i64), ("strideC", _i64),
+        ("stride2A", _i64), ("stride2B", _i64), ("stride2C", _i64),
+        ("alpha", _f32), ("beta", _f32),
+        ("epilogue", ctypes.c_int32), ("tile_n", ctypes.c_int32),
+    ]
+
+
+def _sig(name, argtypes, restype=ctypes.c_int):
+    fn = getattr(_lib, name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+_linear_sig = [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _f32, _f32, _ptr]
+_c_linear_b8_o8 = _sig("ti_linear_a8_w8_b8_o8", _linear_sig)
+_c_linear_relu_b8_o8 = _sig("ti_linear_relu_a8_w8_b8_o8", _linear_sig)
+_c_linear_bfp32_ofp32 = _sig("ti_linear_a8_w8_bfp32_ofp32", _linear_sig)
+_c_linear_b32_o32 = _sig("ti_linear_a8_w8_b32_o32", [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _ptr])
+_c_linear_b32_o32_scaling = _sig("ti_linear_a8_w8_b32_o32_with_scaling", _linear_sig)
+_bmm_sig = [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _f32, _ptr]
+_c_bmm_f32 = _sig("ti_bmm_s8t_s8n_f32t", _bmm_sig)
+_c_bmm_s8 = _sig("ti_bmm_s8t_s8n_s8t", _bmm_sig)
+_c_bmm_s32 = _sig("ti_bmm_s8t_s8n_s32t", [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr])
+_c_gemm_ex = _sig("ti_gemm_i8_ex", [ctypes.POINTER(_GemmDesc), _ptr])
+_c_dq_add_ln_q = _sig("ti_dq_add_layernorm_q",
+                      [_ptr, _f32, _ptr, _i32, _ptr, _ptr, _f32, _ptr, _ptr, _i64, _i64, _ptr])
+_c_dq_add_ln_q_bias = _sig("ti_dq_add_layernorm_q_bias",
+                           [_ptr, _f32, _ptr, _ptr, _i32, _ptr, _ptr, _f32, _ptr, _ptr, _i64, _i64, _ptr])
+_c_ln_q = _sig("ti_layernorm_q", [_ptr, _i32, _ptr, _ptr, _f32, _ptr, _i64, _i64, _ptr])
+_c_softmax_q = _sig("ti_softmax_q", [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _ptr])
+_c_last_error = _sig("ti_last_error", [], ctypes.c_char_p)
+_c_device_status = _sig("ti_device_status", [ctypes.POINTER(ctypes.c_int), _i32])
+_c_abi_version = _sig("ti_abi_version", [])
+
+if _c_abi_version() != 1:
+    raise ImportError("torch_int._CUDA: libtorch_int_b200.so has an unexpected ABI version")
+
+EPI_S8_BIAS_S8, EPI_S8_BIAS_S8_RELU, EPI_F32_BIAS_F32, EPI_S32_BIAS_S32_ADD, \
+    EPI_S32_BIAS_S32_SCALE, EPI_F32_ALPHA, EPI_S8_ALPHA, EPI_S32_RAW = range(8)
+_EPI_OUT_DTYPE = {
+    EPI_S8_BIAS_S8: torch.int8, EPI_S8_BIAS_S8_RELU: torch.int8, EPI_F32_BIAS_F32: torch.float32,
+    EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32,
+    EPI_F32_ALPHA: torch.float32, EPI_S8_ALPHA: torch.int8, EPI_S32_RAW: torch.int32,
+}
+_EPI_BIAS_DTYPE = {
+    EPI_S8_BIAS_S8: torch.int8, EPI_S8_BIAS_S8_RELU: torch.int8, EPI_F32_BIAS_F32: torch.float32,
+    EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32,
+}
+
+
+def _check(rc):
+    if rc != 0:
+        raise RuntimeError("torch_int._CUDA: " + _c_last_error().decode("utf-8", "replace"))
+
+
+def _stream_ptr(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class _on_device:
+    """Makes `device` current for the duration of a call (cheap when it already is)."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+def _require(t, name, dtype, ndim=None):
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (this build has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise RuntimeError(f"{name} must be {ndim}-dimensional, got shape {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
+
+
+def _bias_vector(bias, n, dtype, device):
+    # The reference accepts any bias shape with N elements, on any device
+    # (bias.to(device).view({1,-1}), torch_int/kernels/linear.cu:420).
+    if not isinstance(bias, torch.Tensor):
+        raise RuntimeError("bias must be a torch.Tensor")
+    if bias.dtype != dtype:
+        raise RuntimeError(f"bias must have dtype {dtype}, got {bias.dtype}")
+    if bias.numel() != n:
+        raise RuntimeError(f"bias must have {n} elements, got shape {tuple(bias.shape)}")
+    if bias.device != device:
+        bias = bias.to(device)
+    return bias.reshape(-1).contiguous()
+
+
+def _linear(cfn, x, w, bias, bias_dtype, out_dtype, alpha=None, beta=None):
+    _require(x, "input", torch.int8, 2)
+    _require(w, "weight", torch.int8, 2)
+    if w.device != x.device:
+        raise RuntimeError("input and weight must be on the same device")
+    m, k = x.shape
+    n, kw = w.shape
+    if k != kw:
+        raise RuntimeError(f"input [{m},{k}] and weight [{n},{kw}] disagree on K")
+    b = _bias_vector(bias, n, bias_dtype, x.device)
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    with _on_device(x.device):
+        s = _stream_ptr(x.device)
+        if alpha is None:
+            rc = cfn(x.data_ptr(), w.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, s)
+        else:
+            rc = cfn(x.data_ptr(), w.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k,
+                     float(alpha), float(beta), s)
+    _check(rc)
+    return out
+
+
+def linear_a8_w8_b8_o8(input, weight, bias, alpha, beta):
+    """int8 [M,N] = sat_rne(alpha * (input . weight^T) + beta * bias); bias int8.
+    Reference: torch_int/kernels/linear.cu:369-473."""
+    return _linear(_c_linear_b8_o8, input, weight, bias, torch.int8, torch.int8, alpha, beta)
+
+
+def linear_relu_a8_w8_b8_o8(input, weight, bias, alpha, beta):
+    """As linear_a8_w8_b8_o8 with ReLU before rounding.
+    Reference: torch_int/kernels/linear.cu:476-625."""
+    return _linear(_c_linear_relu_b8_o8, input, weight, bias, torch.int8, torch.int8, alpha, beta)
+
+
+def linear_a8_w8_bfp32_ofp32(input, weight, bias, alpha, beta):
+    """fp32 [M,N] = alpha * (input . weight^T) + beta * bias; bias fp32.
+    Reference: torch_int/kernels/linear.cu:246-365."""
+    return _linear(_c_linear_bfp32_ofp32, input, weight, bias, torch.float32, torch.float32, alpha, beta)
+
+
+def linear_a8_w8_b32_o32(input, weight, bias):
+    """int32 [M,N] = input . weight^T + bias; bias int32.
+    Reference: torch_int/kernels/linear.cu:13-136."""
+    return _linear(_c_linear_b32_o32, input, weight, bias, torch.int32, torch.int32)
+
+
+def linear_a8_w8_b32_o32_with_scaling(input, weight, bias, alpha, beta):
+    """int32 [M,N] = sat_rne(alpha * (input . weight^T) + beta * bias); bias int32.
+    Reference: torch_int/kernels/linear.cu:139-243."""
+    return _linear(_c_linear_b32_o32_scaling, input, weight, bias, torch.int32, torch.int32, alpha, beta)
+
+
+def _bmm(cfn, a, b, out_dtype, alpha=None):
+    _require(a, "A", torch.int8, 3)
+    _require(b, "B", torch.int8, 3)
+    if a.device != b.device:
+        raise RuntimeError("A and B must be on the same device")
+    batch, m, k = a.shape
+    bb, n, kb = b.shape
+    if bb != batch or kb != k:
+        raise RuntimeError(f"A {tuple(a.shape)} and B {tuple(b.shape)} must be [B,M,K] and [B,N,K]")
+    out = torch.empty((batch, m, n), dtype=out_dtype, device=a.device)
+    with _on_device(a.device):
+        s = _stream_ptr(a.device)
+        if alpha is None:
+            rc = cfn(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, m, n, k, s)
+        else:
+            rc = cfn(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, m, n, k, float(alpha), s)
+    _check(rc)
+    return out
+
+
+def bmm_s8t_s8n_s8t(A, B, alpha):
+    """int8 [B,M,N] = sat_rne(alpha * A[b] . B[b]^T).  Reference: torch_int/kernels/bmm.cu:110-208."""
+    return _bmm(_c_bmm_s8, A, B, torch.int8, alpha)
+
+
+def bmm_s8t_s8n_f32t(A, B, alpha):
+    """fp32 [B,M,N] = alpha * A[b] . B[b]^T.  Reference: torch_int/kernels/bmm.cu:10-108."""
+    return _bmm(_c_bmm_f32, A, B, torch.float32, alpha)
+
+
+def bmm_s8t_s8n_s32t(A, B):
+    """int32 [B,M,N] = A[b] . B[b]^T.  Reference: torch_int/kernels/bmm.cu:210-295."""
+    return _bmm(_c_bmm_s32, A, B, torch.int32)
+
+
+def _float_kind(t, name):
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.float16:
+        return 1
+    raise RuntimeError(f"{name} must be float32 or float16, got {t.dtype}")
+
+
+def _affine(gamma, beta, h, device):
+    # gamma/beta are fp32 buffers in the reference modules (torch_int/nn/fused.py:10-11).
+    out = []
+    for t, name in ((gamma, "gamma"), (beta, "beta")):
+        if not isinstance(t, torch.Tensor) or t.numel() != h:
+            raise RuntimeError(f"{name} must be a tensor with {h} elements")
+        t = t.detach()
+        if t.device != device or t.dtype != torch.float32 or not t.is_contiguous():
+            t = t.to(device=device, dtype=torch.float32).contiguous()
+        out.append(t.reshape(-1))
+    return out
+
+
+def dq_add_layernorm_q(input, input_scale, residual_input, gamma, beta, epsilon):
+    """(residual_out, ln_out int8) = dequant-add-LayerNorm-quant in one kernel.
+    Reference: torch_int/kernels/fused.cu:7-25."""
+    return dq_add_layernorm_q_bias(input, input_scale, None, residual_input, gamma, beta, epsilon)
+
+
+def dq_add_layernorm_q_bias(input, input_scale, input_bias, residual_input, gamma, beta, epsilon):
+    """dq_add_layernorm_q with an optional fp32 bias [H] added to the dequantised
+    input before the residual add (no reference counterpart; used after an
+    int32 all-reduce of row-parallel partial sums)."""
+    _require(input, "input", torch.int32)
+    _require(residual_input, "residual_input", None)
+    kind = _float_kind(residual_input, "residual_input")
+    if residual_input.shape != input.shape or input.device != residual_input.device:
+        raise RuntimeError("input and residual_input must have the same shape and device")
+    if input.dim() < 1:
+        raise RuntimeError("input must have at least one dimension")
+    h = input.shape[-1]
+    rows = input.numel() // h if h else 0
+    g, b = _affine(gamma, beta, h, input.device)
+    res_out = torch.empty_like(residual_input)
+    q = torch.empty(input.shape, dtype=torch.int8, device=input.device)
+    with _on_device(input.device):
+        s = _stream_ptr(input.device)
+        if input_bias is None:
+            rc = _c_dq_add_ln_q(input.data_ptr(), float(input_scale), residual_input.data_ptr(), kind,
+                                g.data_ptr(), b.data_ptr(), float(epsilon), res_out.data_ptr(),
+                                q.data_ptr(), rows, h, s)
+        else:
+            ib = _bias_vector(input_bias, h, torch.float32, input.device)
+            rc = _c_dq_add_ln_q_bias(input.data_ptr(), float(input_scale), ib.data_ptr(),
+                                     residual_input.data_ptr(), kind, g.data_ptr(), b.data_ptr(),
+                                     float(epsilon), res_out.data_ptr(), q.data_ptr(), rows, h, s)
+    _check(rc)
+    return res_out, q
+
+
+def layernorm_q(x, gamma, beta, epsilon):
+    """int8 = clamp(rne(LayerNorm(x) * gamma + beta)) in one kernel.
+    Reference: LayerNormQ.forward, torch_int/nn/fused.py:13-18."""
+    _require(x, "x", None)
+    kind = _float_kind(x, "x")
+    h = x.shape[-1]
+    rows = x.numel() // h if h else 0
+    g, b = _affine(gamma, beta, h, x.device)
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    with _on_device(x.device):
+        rc = _c_ln_q(x.data_ptr(), kind, g.data_ptr(), b.data_ptr(), float(epsilon), q.data_ptr(),
+                     rows, h, _stream_ptr(x.device))
+    _check(rc)
+    return q
+
+
+def softmax_q(scores, mask=None, num_heads=1, causal=-1):
+    """int8 probs = rne(127 * softmax(max(scores + mask, finfo.min))) over the last dim.
+    scores fp32 [B*H, T, S]; mask: additive fp32 [B, 1, T, S] / [B, T, S] or None;
+    causal >= 0 generates "column j visible iff j <= t + causal" instead.
+    Reference: torch_int/models/opt.py:139-178."""
+    _require(scores, "scores", torch.float32, 3)
+    bh, t, s = scores.shape
+    mptr = None
+    if mask is not None:
+        _require(mask, "mask", torch.float32)
+        if mask.numel() != (bh // num_heads) * t * s or bh % num_heads != 0:
+            raise RuntimeError(f"mask shape {tuple(mask.shape)} does not match scores {tuple(scores.shape)} "
+                               f"with {num_heads} heads")
+        mptr = mask.data_ptr()
+    out = torch.empty((bh, t, s), dtype=torch.int8, device=scores.device)
+    with _on_device(scores.device):
+        rc = _c_softmax_q(scores.data_ptr(), mptr, out.data_ptr(), bh, num_heads, t, s, s, s,
+                          int(causal), _stream_ptr(scores.device))
+    _check(rc)
+    return out
+
+
+def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, lda, ldb, ldc,
+               stride_a=0, stride_b=0, stride_c=0, stride2_a=0, stride2_b=0, stride2_c=0,
+               alpha=1.0, beta=0.0, tile_n=0):
+    """Strided form (ti_gemm_i8_ex): operands are addressed through explicit
+    element strides starting at each tensor's data pointer, so views can be
+    multiplied without contiguous copies.  Writes into `out` and returns it."""
+    for t, name in ((a, "a"), (b, "b")):
+        if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.int8):
+            raise RuntimeError(f"{name} must be a CUDA int8 tensor")
+    if not (isinstance(out, torch.Tensor) and out.is_cuda and out.dtype == _EPI_OUT_DTYPE[epilogue]):
+        raise RuntimeError(f"out must be a CUDA tensor of dtype {_EPI_OUT_DTYPE[epilogue]}")
+    if a.device != b.device or a.device != out.device:
+        raise RuntimeError("a, b and out must be on the same device")
+
+    def _span(mm, kk, ld, nb, st, nb2, st2):
+        return (mm - 1) * ld + kk + (nb - 1) * st + (nb2 - 1) * st2 if min(mm, kk, nb, nb2) > 0 else 0
+
+    if _span(m, k, lda, batch, stride_a, batch2, stride2_a) > a.untyped_storage().nbytes() - a.storage_offset():
+        raise RuntimeError("a: strides address memory beyond the tensor's storage")
+    if _span(n, k, ldb, batch, stride_b, batch2, stride2_b) > b.untyped_storage().nbytes() - b.storage_offset():
+        raise RuntimeError("b: strides address memory beyond the tensor's storage")
+    if _span(m, n, ldc, batch, stride_c, batch2, stride2_c) > \
+            out.untyped_storage().nbytes() // out.element_size() - out.storage_offset():
+        raise RuntimeError("out: strides address memory beyond the tensor's storage")
+    d = _GemmDesc()
+    d.A, d.B, d.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    if epilogue in _EPI_BIAS_DTYPE:
+        bv = _bias_vector(bias, n, _EPI_BIAS_DTYPE[epilogue], a.device)
+        d.bias = bv.data_ptr()
+    else:
+        d.bias = None
+    d.M, d.N, d.K, d.batch, d.batch2 = m, n, k, batch, batch2
+    d.lda, d.ldb, d.ldc = lda, ldb, ldc
+    d.strideA, d.strideB, d.strideC = stride_a, stride_b, stride_c
+    d.stride2A, d.stride2B, d.stride2C = stride2_a, stride2_b, stride2_c
+    d.alpha, d.beta, d.epilogue, d.tile_n = float(alpha), float(beta), epilogue, tile_n
+    with _on_device(a.device):
+        rc = _c_gemm_ex(ctypes.byref(d), _stream_ptr(a.device))
+    _check(rc)
+    return out
+
+
+def device_status(reset=True):
+    """Synchronises the current device and returns the kernels' status word
+    (0 = ok; otherwise the code of the first in-kernel wait that timed out)."""
+    v = ctypes.c_int(0)
+    _check(_c_device_status(ctypes.byref(v), 1 if reset else 0))
+    return v.value
