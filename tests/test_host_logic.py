@@ -1,0 +1,96 @@
+"""Host-side behaviour of the torch_int package that needs no GPU: module
+surface, buffer names, from_float arithmetic, and loud failure without CUDA."""
+import pytest
+import torch
+
+import torch_int  # noqa: F401
+from torch_int import _CUDA
+from torch_int.nn.bmm import BMM_S8T_S8N_F32T, BMM_S8T_S8N_S8T, BMM_S8T_S8N_S32T
+from torch_int.nn.fused import DQ_Add_LayerNorm_Q, LayerNormQ
+from torch_int.nn.linear import (W8A8B8O8Linear, W8A8B8O8LinearReLU, W8A8B32O32Linear,
+                                 W8A8B32O32LinearWithoutScaling, W8A8BFP32OFP32Linear, W8A16Linear,
+                                 W8FakeA8Linear)
+
+
+def test_reference_callables_exist():
+    # torch_int/kernels/bindings.cpp:5-20
+    for name in ("linear_relu_a8_w8_b8_o8", "linear_a8_w8_b32_o32", "linear_a8_w8_bfp32_ofp32",
+                 "linear_a8_w8_b32_o32_with_scaling", "linear_a8_w8_b8_o8", "dq_add_layernorm_q",
+                 "bmm_s8t_s8n_s8t", "bmm_s8t_s8n_f32t", "bmm_s8t_s8n_s32t"):
+        assert callable(getattr(_CUDA, name))
+    assert torch_int.nn.W8A16Linear is W8A16Linear and torch_int.nn.W8FakeA8Linear is W8FakeA8Linear
+
+
+def test_buffer_names_shapes_dtypes():
+    # torch_int/nn/linear.py:23-28,112-115,189-193; nn/bmm.py:8; nn/fused.py:10-11
+    m = W8A8B8O8Linear(32, 48, alpha=0.5, beta=0.25)
+    sd = m.state_dict()
+    assert list(sd) == ["weight", "bias", "a", "b"]
+    assert sd["weight"].shape == (48, 32) and sd["weight"].dtype == torch.int8
+    assert sd["bias"].shape == (1, 48) and sd["bias"].dtype == torch.int8
+    assert sd["a"].dim() == 0 and float(sd["a"]) == 0.5 and float(sd["b"]) == 0.25
+    assert list(W8A8B8O8LinearReLU(32, 48).state_dict()) == ["weight", "bias", "a", "b"]
+    assert list(W8A8B32O32LinearWithoutScaling(32, 48).state_dict()) == ["weight", "bias"]
+    assert W8A8B32O32Linear(32, 48).bias.dtype == torch.int32
+    f = W8A8BFP32OFP32Linear(32, 48)
+    assert list(f.state_dict()) == ["weight", "bias", "a"] and f.bias.dtype == torch.float32
+    f.half()
+    assert f.bias.dtype == torch.float32, "the fp32 bias must survive .half() (nn/linear.py:195-206)"
+    assert list(BMM_S8T_S8N_S8T(1.0).state_dict()) == ["a"]
+    assert list(BMM_S8T_S8N_S32T().state_dict()) == []
+    assert list(LayerNormQ(8).state_dict()) == ["weight", "bias"]
+    assert list(DQ_Add_LayerNorm_Q(8).state_dict()) == ["weight", "bias"]
+    assert W8A16Linear(8, 4).weight_scales.dtype == torch.float16
+    assert W8FakeA8Linear(8, 4, act_quant="per_tensor").bias.shape == (1, 4)
+
+
+def test_from_float_scale_folding_and_no_mutation():
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(64, 32)
+    w0, b0 = lin.weight.detach().clone(), lin.bias.detach().clone()
+    q = W8A8B8O8Linear.from_float(lin, input_scale=0.02, output_scale=0.05)
+    assert torch.equal(lin.weight, w0) and torch.equal(lin.bias, b0), "from_float must not modify the float module"
+    ws = w0.abs().max() / 127
+    bs = b0.abs().max() / 127
+    assert torch.equal(q.weight, (w0 / ws).round().to(torch.int8))          # nn/linear.py:49
+    assert torch.allclose(q.a, 0.02 * ws / 0.05) and torch.allclose(q.b, bs / 0.05)  # :51-52
+    q = W8A8BFP32OFP32Linear.from_float(lin, input_scale=0.02)
+    assert torch.allclose(q.a, 0.02 * ws) and torch.equal(q.bias.reshape(-1), b0)   # :224-226
+    q = W8A8B32O32Linear.from_float(lin, 0.02, 0.05)
+    assert q.bias.dtype == torch.int32 and torch.allclose(q.b, (b0.abs().max() / (2 ** 31 - 1)) / 0.05)
+    ln = torch.nn.LayerNorm(64)
+    ln.weight.data.uniform_(0.5, 1.5)
+    lq = LayerNormQ.from_float(ln, 0.1)
+    assert torch.allclose(lq.weight, ln.weight / 0.1) and lq.eps == ln.eps           # nn/fused.py:24-26
+    bm = BMM_S8T_S8N_S8T.from_scale(0.1, 0.2, 0.4)
+    assert abs(float(bm.a) - 0.05) < 1e-7                                            # nn/bmm.py:19-23
+    bm = BMM_S8T_S8N_F32T.from_scale(torch.tensor(0.1), 0.2)
+    assert abs(float(bm.a) - 0.02) < 1e-7
+
+
+def test_scalar_cache_follows_buffer_updates():
+    m = W8A8B8O8Linear(16, 16, alpha=2.0, beta=3.0)
+    assert m._scalar("a") == 2.0
+    m.a = torch.tensor(5.0)
+    assert m._scalar("a") == 5.0
+    m.a.fill_(7.0)
+    assert m._scalar("a") == 7.0
+    m.load_state_dict({**m.state_dict(), "a": torch.tensor(9.0)})
+    assert m._scalar("a") == 9.0
+
+
+def test_no_cpu_fallback():
+    """The product must fail loudly, not compute on the CPU."""
+    x = torch.zeros((4, 16), dtype=torch.int8)
+    w = torch.zeros((16, 16), dtype=torch.int8)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _CUDA.linear_a8_w8_b8_o8(x, w, torch.zeros(16, dtype=torch.int8), 1.0, 1.0)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _CUDA.bmm_s8t_s8n_s32t(x[None], w[None])
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        W8A8B8O8Linear(16, 16)(x)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        LayerNormQ(16)(torch.zeros(2, 16))
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _CUDA.dq_add_layernorm_q(torch.zeros((2, 16), dtype=torch.int32), 0.1, torch.zeros(2, 16),
+                                 torch.ones(16), torch.zeros(16), 1e-5)

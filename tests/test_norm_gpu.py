@@ -1,0 +1,99 @@
+"""Parity of the LayerNorm-quantise, dequant-add-LayerNorm-quantise and softmax-quantise
+kernels with the CPU oracle (which calls the same torch functions the reference calls)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_fp32_close, assert_quant_close, randn
+from oracle import w8a8 as O
+
+pytestmark = pytest.mark.gpu
+
+
+def affine(h, seed, scale):
+    g = torch.Generator().manual_seed(seed)
+    return (1.0 + 0.1 * torch.randn(h, generator=g)) * scale, 0.1 * torch.randn(h, generator=g) * scale
+
+
+def test_layernorm_q_golden(cuda_ops, golden_dir):
+    z = np.load(os.path.join(golden_dir, "layernorm_q.npz"))  # reference LayerNormQ.forward outputs
+    for i in range(int(z["n"])):
+        q = cuda_ops.layernorm_q(torch.from_numpy(z[f"x{i}"]).cuda(), torch.from_numpy(z[f"gamma{i}"]).cuda(),
+                                 torch.from_numpy(z[f"beta{i}"]).cuda(), float(z[f"eps{i}"]))
+        assert_quant_close(q, torch.from_numpy(z[f"q{i}"]), 0.999, f"golden case {i}")
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 4), (2, 3, 8), (3, 7, 100), (2, 5, 1026), (4, 512, 5120), (2, 64, 7168),
+                                   (1, 32, 12288), (1, 3, 20480)])
+def test_layernorm_q_vs_oracle(cuda_ops, shape):
+    from torch_int.nn.fused import LayerNormQ
+    h = shape[-1]
+    x = randn(shape, 1, 2.0) + 0.3
+    gamma, beta = affine(h, 2, 25.0)
+    m = LayerNormQ(h)
+    m.weight, m.bias = gamma, beta
+    m = m.cuda()
+    assert_quant_close(m(x.cuda()), O.layernorm_q(x, gamma, beta, 1e-5), 0.999, str(shape))
+    assert_quant_close(m(x.half().cuda()), O.layernorm_q(x.half(), gamma, beta, 1e-5), 0.999, str(shape) + " fp16 in")
+
+
+def test_dq_add_layernorm_q_golden(cuda_ops, golden_dir):
+    z = np.load(os.path.join(golden_dir, "dq_add_layernorm_q.npz"))  # reference dq_add_layernorm_q_py outputs
+    for i in range(int(z["n"])):
+        r, q = cuda_ops.dq_add_layernorm_q(torch.from_numpy(z[f"in{i}"]).cuda(), float(z[f"scale{i}"]),
+                                           torch.from_numpy(z[f"res{i}"]).cuda(),
+                                           torch.from_numpy(z[f"gamma{i}"]).cuda(),
+                                           torch.from_numpy(z[f"beta{i}"]).cuda(), float(z[f"eps{i}"]))
+        assert_fp32_close(r, torch.from_numpy(z[f"res_out{i}"]), 1e-5, f"residual, golden case {i}")
+        assert_quant_close(q, torch.from_numpy(z[f"q{i}"]), 0.999, f"q, golden case {i}")
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 4), (1, 5, 90), (4, 512, 5120), (2, 128, 12288), (1, 2, 16388)])
+def test_dq_add_layernorm_q_vs_oracle(cuda_ops, shape):
+    h = shape[-1]
+    g = torch.Generator().manual_seed(3)
+    x = torch.randint(-200000, 200000, shape, generator=g, dtype=torch.int32)
+    res = randn(shape, 4)
+    gamma, beta = affine(h, 5, 30.0)
+    scale = 1.3e-5
+    r, q = cuda_ops.dq_add_layernorm_q(x.cuda(), scale, res.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+    r_o, q_o = O.dq_add_layernorm_q(x, scale, res, gamma, beta, 1e-5)
+    assert torch.equal(r.cpu(), r_o), "residual output must be bit-exact (one fused multiply-add)"
+    assert_quant_close(q, q_o, 0.999, str(shape))
+    # the input tensors are not modified (fused.cu:17 uses an out-of-place add)
+    assert torch.equal(res, randn(shape, 4))
+    bias = randn((h,), 6, 0.5)
+    r, q = cuda_ops.dq_add_layernorm_q_bias(x.cuda(), scale, bias.cuda(), res.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+    r_o, q_o = O.dq_add_layernorm_q_bias(x, scale, bias, res, gamma, beta, 1e-5)
+    assert_fp32_close(r, r_o, 1e-6, "residual with bias")
+    assert_quant_close(q, q_o, 0.999, str(shape) + " with bias")
+
+
+def test_dq_add_module(cuda_ops):
+    from torch_int.nn.fused import DQ_Add_LayerNorm_Q
+    m = DQ_Add_LayerNorm_Q(256).cuda()
+    m.input_scale = 0.002
+    g = torch.Generator().manual_seed(7)
+    x = torch.randint(-65536, 65536, (2, 9, 256), generator=g, dtype=torch.int32)
+    res = randn((2, 9, 256), 8)
+    r, q = m(res.cuda(), x.cuda())
+    r_o, q_o = O.dq_add_layernorm_q(x, 0.002, res, torch.ones(256), torch.zeros(256), 1e-5)
+    assert torch.equal(r.cpu(), r_o)
+    assert_quant_close(q, q_o, 0.999)
+
+
+@pytest.mark.parametrize("bsz,heads,t,s", [(1, 1, 1, 16), (2, 3, 16, 16), (2, 4, 48, 112), (1, 5, 512, 512),
+                                           (1, 2, 16, 2048), (2, 2, 1, 528)])
+def test_softmax_q(cuda_ops, bsz, heads, t, s):
+    scores = randn((bsz * heads, t, s), 9, 2.5)
+    mask = O.causal_mask(bsz, t, s)
+    want = O.softmax_q(scores, mask)
+    assert_quant_close(cuda_ops.softmax_q(scores.cuda(), mask.cuda(), heads), want, 0.999, "explicit mask")
+    assert_quant_close(cuda_ops.softmax_q(scores.cuda(), None, heads, causal=s - t), want, 0.999, "generated mask")
+    assert_quant_close(cuda_ops.softmax_q(scores.cuda()), O.softmax_q(scores), 0.999, "no mask")
+    # padding mask: a fully masked key column range
+    pad = mask.clone()
+    pad[:, :, :, : s // 4] = torch.finfo(torch.float32).min
+    assert_quant_close(cuda_ops.softmax_q(scores.cuda(), pad.cuda(), heads), O.softmax_q(scores, pad), 0.999, "padding")
