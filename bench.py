@@ -153,7 +153,7 @@ class GemmWorkload:
                 "frac": round(achieved / peak, 4), "traffic": None,
                 "peak_source": f"2 x cuBLAS bf16 burst of MEASURED_PEAKS.json ({peaks['source']}): "
                                "kind::i8 issues at twice the kind::f16 rate",
-                "kernel": "gemm_i8_kernel<256, EPI_S8_BIAS_S8>",
+                "kernel": "gemm_i8_kernel<256, EPI_S8_BIAS_S8, PAIR=true> (256x256 tiles on CTA pairs)",
                 "frac_of_nominal_4500": round(achieved / 4500.0, 4)}
 
     def cpu_sample(self):
@@ -253,11 +253,13 @@ def run_reference(args, world, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="kernel-only run for ncu: no end-to-end leg, no CPU baseline")
     args = ap.parse_args()
     world, rank, local = dist_env()
     if args.impl == "reference":
@@ -280,7 +282,7 @@ def main():
         sampler.start()
     ms = time_steps(wl.step, args.steps, args.warmup, world)
     clocks = sampler.stop() if sampler else None
-    ms_e2e = time_steps(wl.step_e2e, args.steps, args.warmup, world)
+    ms_e2e = ms if args.profile else time_steps(wl.step_e2e, args.steps, args.warmup, world)
     from torch_int import _CUDA as C
     status = C.device_status()
     assert status == 0, f"a kernel reported wait timeout {status}"
@@ -295,7 +297,7 @@ def main():
                         "ms_per_step": round(ms_e2e, 4)},
                 "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks,
                 "roofline": wl.roofline(ms, peaks)}
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.profile:
             line["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -112,6 +112,7 @@ typedef struct ti_gemm_desc {
   float alpha, beta;
   int32_t epilogue; /* enum ti_epilogue */
   int32_t tile_n;   /* 0 = automatic; else 32, 64, 128 or 256 */
+  int32_t cta_pair; /* 0 = automatic; 1 = single-CTA tiles; 2 = 256x256 tiles on CTA pairs (tile_n 0 or 256) */
 } ti_gemm_desc;
 
 /* The reference has no strided entry point: its wrappers assume packed tensors

@@ -74,15 +74,22 @@ def test_ragged_tiles(cuda_ops, m, n, k):
     run_all(cuda_ops, x, w, b8, b32, bf, 1.0 / (60.0 * k ** 0.5), 0.01, f"{m}x{n}x{k}")
 
 
-@pytest.mark.parametrize("tile_n", [32, 64, 128, 256])
-def test_every_tile_width(cuda_ops, tile_n):
+@pytest.mark.parametrize("tile_n,cta_pair", [(32, 1), (64, 1), (128, 1), (256, 1), (256, 2)])
+def test_every_tile_shape(cuda_ops, tile_n, cta_pair):
+    """Every N tile width of the single-CTA kernel and the 256 x 256 CTA-pair kernel."""
     C = cuda_ops
-    m, n, k = 200, 400, 272
+    m, n, k = 600, 400, 272
     x, w, b8 = rand_s8((m, k), 20), rand_s8((n, k), 21), rand_s8((n,), 22)
     out = torch.empty((m, n), dtype=torch.int8, device="cuda")
     C.gemm_i8_ex(x.cuda(), w.cuda(), out, b8.cuda(), epilogue=C.EPI_S8_BIAS_S8, m=m, n=n, k=k,
-                 lda=k, ldb=k, ldc=n, alpha=0.002, beta=0.05, tile_n=tile_n)
-    assert_bit_exact(out, O.linear_a8_w8_b8_o8(x, w, b8, 0.002, 0.05), f"tile_n={tile_n}")
+                 lda=k, ldb=k, ldc=n, alpha=0.002, beta=0.05, tile_n=tile_n, cta_pair=cta_pair)
+    assert_bit_exact(out, O.linear_a8_w8_b8_o8(x, w, b8, 0.002, 0.05), f"tile_n={tile_n} cta_pair={cta_pair}")
+    bf = randn((n,), 23)
+    outf = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    C.gemm_i8_ex(x.cuda(), w.cuda(), outf, bf.cuda(), epilogue=C.EPI_F32_BIAS_F32, m=m, n=n, k=k,
+                 lda=k, ldb=k, ldc=n, alpha=0.002, beta=1.0, tile_n=tile_n, cta_pair=cta_pair)
+    assert_fp32_close(outf, O.linear_a8_w8_bfp32_ofp32(x, w, bf, 0.002, 1.0), 1e-5, f"fp32 tile_n={tile_n}")
+    assert C.device_status() == 0
 
 
 def test_config_single_linear(cuda_ops):

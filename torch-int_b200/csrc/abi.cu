@@ -121,6 +121,10 @@ int ti_gemm_i8_ex(const ti_gemm_desc* d, void* stream) {
     set_error("ti_gemm_i8_ex: tile_n must be 0, 32, 64, 128 or 256");
     return TI_E_INVALID;
   }
+  if (d->cta_pair < 0 || d->cta_pair > 2) {
+    set_error("ti_gemm_i8_ex: cta_pair must be 0, 1 or 2");
+    return TI_E_INVALID;
+  }
   GemmProblem g;
   g.A = d->A;
   g.B = d->B;
@@ -144,6 +148,7 @@ int ti_gemm_i8_ex(const ti_gemm_desc* d, void* stream) {
   g.beta = d->beta;
   g.epilogue = d->epilogue;
   g.force_bn = d->tile_n;
+  g.force_pair = d->cta_pair;
   return launch_gemm_i8(g, static_cast<cudaStream_t>(stream));
 }
 

@@ -37,7 +37,8 @@ struct GemmProblem {
   int64_t stride2A = 0, stride2B = 0, stride2C = 0;  // per `batch2` index
   float alpha = 1.f, beta = 0.f;
   int epilogue = EPI_S32_RAW;
-  int force_bn = 0;  // 0 = choose the N tile automatically
+  int force_bn = 0;    // 0 = choose the N tile automatically
+  int force_pair = 0;  // 0 = automatic, 1 = single-CTA tiles only, 2 = CTA-pair tiles (256 x 256)
 };
 
 // Returns 0 or a negative TI_E_* code (message via set_error()).

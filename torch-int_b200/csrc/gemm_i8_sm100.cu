@@ -53,16 +53,25 @@ struct KernelParams {
   int group_m;              // rasterisation: M tiles per column sweep
 };
 
-template <int BN>
+// PAIR = false: one CTA computes a 128 x BN tile (tcgen05 cta_group::1).
+// PAIR = true : two CTAs of a cluster compute a 256 x BN tile together
+//               (cta_group::2): each loads its own 128 rows of A and its own
+//               BN/2 rows of B, the leader CTA issues M=256 MMAs that read both
+//               CTAs' shared memory and write 128 accumulator rows into each
+//               CTA's TMEM.  Per CTA this halves the B bytes that TMA writes to
+//               and the tensor core reads from shared memory.
+template <int BN, bool PAIR>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK;
-  static constexpr int B_BYTES = BN * BK;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
+  static constexpr int B_BYTES = B_ROWS * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int AUX_BYTES = 2 * BN * 4 + 256;  // bias tiles + barriers
   static constexpr int STAGES_RAW = (SMEM_BUDGET - 1024 - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32..256, multiple of 32");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
   static_assert(STAGES >= 2, "need at least two stages");
@@ -139,12 +148,13 @@ __device__ __forceinline__ uint32_t epilogue_one(uint32_t acc_bits, uint32_t t, 
   }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const KernelParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PAIR>;
   using T = EpiTraits<EPI>;
+  constexpr int CG = PAIR ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   // 128B-swizzled tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -152,15 +162,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* aux = smem + C::STAGES * C::STAGE_BYTES;
   uint32_t* bias_smem = reinterpret_cast<uint32_t*>(aux);  // [2][BN]
   uint64_t* bars = reinterpret_cast<uint64_t*>(aux + 2 * BN * 4);
-  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* full_bar = bars;                    // [STAGES]  (PAIR: only the leader's are used)
   uint64_t* empty_bar = bars + C::STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * C::STAGES;   // [2]
-  uint64_t* tempty_bar = tfull_bar + 2;         // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;         // [2]       (PAIR: only the leader's are used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0;  // 0 = leader of the CTA pair
+  const long long first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const long long tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -169,7 +182,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tfull_bar[b]), 1);
-      mbar_init(smem_u32(&tempty_bar[b]), EPI_THREADS / 32);
+      mbar_init(smem_u32(&tempty_bar[b]), (PAIR ? 2 : 1) * (EPI_THREADS / 32));
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -177,11 +190,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(tmem_slot), C::TMEM_COLS);
-    tmem_relinquish<1>();
+    tmem_alloc<CG>(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish<CG>();
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR)
+    cluster_sync_all();  // the peer's barriers must be initialised before any remote arrive
+  else
+    __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -191,16 +207,32 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step) {
         const TileCoord tc = decode_tile(t, p);
+        const int row_a = tc.m_tile * C::TILE_M + static_cast<int>(rank) * BM;
+        const int row_b = tc.n_tile * BN + static_cast<int>(rank) * C::B_ROWS;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, TI_ERR_WAIT_EMPTY);
           if (!ok) break;
-          const uint32_t fb = smem_u32(&full_bar[stage]);
-          mbar_expect_tx(fb, C::STAGE_BYTES);
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
-          tma_load_4d(smem_u32(sa), &tmap_a, fb, kb * BK, tc.m_tile * BM, tc.b1, tc.b2);
-          tma_load_4d(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, tc.n_tile * BN, tc.b1, tc.b2);
+          if constexpr (PAIR) {
+            // Both CTAs' loads count their bytes on the LEADER's barrier, which
+            // therefore completes when the operands of the whole 256-row MMA are in
+            // place.  Only the leader arrives on it, expecting the bytes of both CTAs
+            // (the peer's bytes may be counted before or after that arrive; the phase
+            // cannot complete until the arrive has happened).  A remote
+            // arrive.expect_tx with cluster-scope release from the peer was measured
+            // to halve the throughput of the whole kernel.
+            const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
+            if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * C::STAGE_BYTES);
+            tma_load_4d_pair(smem_u32(sa), &tmap_a, fb, kb * BK, row_a, tc.b1, tc.b2);
+            tma_load_4d_pair(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, row_b, tc.b1, tc.b2);
+          } else {
+            const uint32_t fb = smem_u32(&full_bar[stage]);
+            mbar_expect_tx(fb, C::STAGE_BYTES);
+            tma_load_4d(smem_u32(sa), &tmap_a, fb, kb * BK, row_a, tc.b1, tc.b2);
+            tma_load_4d(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, row_b, tc.b1, tc.b2);
+          }
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1;
@@ -210,16 +242,16 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_s8s8s32(BM, BN);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_s8s8s32(C::TILE_M, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+      for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
         const int buf = it & 1;
-        ok = mbar_wait(smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1, abort_flag,
-                       TI_ERR_WAIT_TMEM_EMPTY);
+        ok = mbar_wait<PAIR>(smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1, abort_flag,
+                             TI_ERR_WAIT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
@@ -234,15 +266,26 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // +32 bytes of K inside the 128-byte swizzle row = +2 in the
             // (address >> 4) field of the descriptor.
-            umma_i8<1>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_i8<CG>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
           }
-          umma_commit(smem_u32(&empty_bar[stage]));
+          // Hand the stage back to the producer(s) once these MMAs have read it.
+          if constexpr (PAIR) {
+            umma_commit_pair_both(smem_u32(&empty_bar[stage]));
+          } else {
+            umma_commit(smem_u32(&empty_bar[stage]));
+          }
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) umma_commit(smem_u32(&tfull_bar[buf]));
+        if (ok) {
+          if constexpr (PAIR) {
+            umma_commit_pair_both(smem_u32(&tfull_bar[buf]));
+          } else {
+            umma_commit(smem_u32(&tfull_bar[buf]));
+          }
+        }
       }
     }
   } else {
@@ -251,7 +294,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int et = threadIdx.x - 64;
     int it = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+    for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
       const TileCoord tc = decode_tile(t, p);
       const int buf = it & 1;
       const int n0 = tc.n_tile * BN;
@@ -279,7 +322,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!ok) break;
       tc_fence_after();
 
-      const int row = tc.m_tile * BM + quarter * 32 + lane;
+      const int row = tc.m_tile * C::TILE_M + static_cast<int>(rank) * BM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       uint8_t* crow = static_cast<uint8_t*>(p.C) +
                       (static_cast<long long>(tc.b2) * p.stride2C +
@@ -330,25 +373,38 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[buf]));
+      if (lane == 0) {
+        if constexpr (PAIR)
+          mbar_arrive_remote(mapa_shared(smem_u32(&tempty_bar[buf]), 0));
+        else
+          mbar_arrive(smem_u32(&tempty_bar[buf]));
+      }
     }
   }
 
   // ------------------------------------------------------------------ teardown
   __syncwarp();
   tc_fence_before();
-  __syncthreads();
+  // In a CTA pair neither CTA may release shared memory or TMEM while the other
+  // can still signal its barriers or the leader's MMAs can still read its tiles.
+  if constexpr (PAIR)
+    cluster_sync_all();
+  else
+    __syncthreads();
   if (*abort_flag) {
     // A wait gave up: give copies and MMAs that may still be in flight a bounded
     // grace period before shared memory and TMEM are released.
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) {
     }
-    __syncthreads();
   }
+  if constexpr (PAIR)
+    cluster_sync_all();
+  else
+    __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, C::TMEM_COLS);
+    tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -412,14 +468,14 @@ int num_sms() {
   return cached[dev];
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR>
 int launch_one(const GemmProblem& g, cudaStream_t stream) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PAIR>;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI, PAIR>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
@@ -430,7 +486,7 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
   CUtensorMap ta, tb;
   if (!make_operand_map(&ta, g.A, g.K, g.M, g.batch, g.batch2, g.lda, g.strideA, g.stride2A, BM))
     return TI_E_CUDA;
-  if (!make_operand_map(&tb, g.B, g.K, g.N, g.batch, g.batch2, g.ldb, g.strideB, g.stride2B, BN))
+  if (!make_operand_map(&tb, g.B, g.K, g.N, g.batch, g.batch2, g.ldb, g.strideB, g.stride2B, C::B_ROWS))
     return TI_E_CUDA;
   KernelParams p;
   p.C = g.C;
@@ -439,7 +495,7 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
   p.N = static_cast<int>(g.N);
   p.K = static_cast<int>(g.K);
   p.num_kb = static_cast<int>((g.K + BK - 1) / BK);
-  p.m_tiles = static_cast<int>((g.M + BM - 1) / BM);
+  p.m_tiles = static_cast<int>((g.M + C::TILE_M - 1) / C::TILE_M);
   p.n_tiles = static_cast<int>((g.N + BN - 1) / BN);
   p.batch = static_cast<int>(g.batch);
   p.batch2 = static_cast<int>(g.batch2);
@@ -449,54 +505,82 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
   p.total_tiles = static_cast<long long>(p.m_tiles) * p.n_tiles * g.batch * g.batch2;
   p.alpha = g.alpha;
   p.beta = g.beta;
-  p.group_m = 16;
+  p.group_m = PAIR ? 8 : 16;
   const int sms = num_sms();
-  const int grid = static_cast<int>(p.total_tiles < sms ? p.total_tiles : sms);
-  gemm_i8_kernel<BN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
-  cudaError_t e = cudaGetLastError();
+  const long long workers = PAIR ? sms / 2 : sms;  // CTAs, or CTA pairs
+  const int grid = static_cast<int>(p.total_tiles < workers ? p.total_tiles : workers) * (PAIR ? 2 : 1);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_kernel<BN, EPI, PAIR>, ta, tb, p);
   if (e != cudaSuccess) {
-    set_error("gemm_i8_kernel<%d,%d> launch failed: %s", BN, EPI, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    set_error("gemm_i8_kernel<%d,%d,%d> launch failed: %s", BN, EPI, PAIR ? 1 : 0, cudaGetErrorString(e));
     return TI_E_CUDA;
   }
   return TI_OK;
 }
 
 template <int EPI>
-int launch_bn(const GemmProblem& g, int bn, cudaStream_t stream) {
+int launch_bn(const GemmProblem& g, int bn, bool pair, cudaStream_t stream) {
+  if (pair) return launch_one<256, EPI, true>(g, stream);
   switch (bn) {
-    case 256: return launch_one<256, EPI>(g, stream);
-    case 128: return launch_one<128, EPI>(g, stream);
-    case 64: return launch_one<64, EPI>(g, stream);
-    case 32: return launch_one<32, EPI>(g, stream);
+    case 256: return launch_one<256, EPI, false>(g, stream);
+    case 128: return launch_one<128, EPI, false>(g, stream);
+    case 64: return launch_one<64, EPI, false>(g, stream);
+    case 32: return launch_one<32, EPI, false>(g, stream);
   }
   set_error("unsupported N tile %d", bn);
   return TI_E_INVALID;
 }
 
-// Pick the N tile: the cost of a configuration is (waves over the SMs) x (time
-// of one k-block of that tile shape).  A k-block is four M=128 MMAs, each
-// bound either by the tensor pipe (N/2 cycles) or by reading A (4 KB) and B
-// (32*N bytes) from shared memory at 128 B/cycle.
-int choose_bn(const GemmProblem& g) {
+// Pick the tile shape.  The cost of a configuration is (waves over the SMs) x
+// (cycles one 32-byte K slice of one tile takes).  A slice is bound either by
+// the tensor pipe (N/2 cycles for 128 rows) or by shared-memory bandwidth
+// (128 B/cycle, shared by the TMA writes and the tensor core's reads of A and
+// B).  The CTA-pair form does 256 rows per slice with only half of B per CTA.
+void choose_tile(const GemmProblem& g, int* bn_out, bool* pair_out) {
   const int cands[4] = {256, 128, 64, 32};
   const int sms = num_sms();
   const long long m_tiles = (g.M + BM - 1) / BM;
+  const long long nb = g.batch * g.batch2;
   double best = 1e300;
   int best_bn = 256;
+  bool best_pair = false;
   for (int i = 0; i < 4; ++i) {
     const int bn = cands[i];
     if (bn > 32 && bn / 2 >= g.N) continue;  // tile mostly padding
-    const long long tiles = m_tiles * ((g.N + bn - 1) / bn) * g.batch * g.batch2;
+    const long long tiles = m_tiles * ((g.N + bn - 1) / bn) * nb;
     const long long waves = (tiles + sms - 1) / sms;
     const double mma = bn / 2.0;
-    const double smem = (4096.0 + 32.0 * bn) / 128.0;
+    const double smem = 2.0 * (4096.0 + 32.0 * bn) / 128.0;
     const double cost = static_cast<double>(waves) * (mma > smem ? mma : smem);
     if (cost < best * 0.999) {
       best = cost;
       best_bn = bn;
     }
   }
-  return best_bn;
+  if (g.force_pair != 1 && g.M > BM && g.N > 128) {
+    const long long tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + 255) / 256) * nb;
+    const long long pairs = sms / 2;
+    const long long waves = (tiles + pairs - 1) / pairs;
+    const double cost = static_cast<double>(waves) * 128.0;  // mma 128 = smem 2*(4096+4096)/128
+    if (cost < best * 1.001 || g.force_pair == 2) {
+      best_bn = 256;
+      best_pair = true;
+    }
+  }
+  *bn_out = best_bn;
+  *pair_out = best_pair;
 }
 
 }  // namespace
@@ -556,16 +640,23 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
     set_error("dimension too large");
     return TI_E_INVALID;
   }
-  int bn = g.force_bn ? g.force_bn : choose_bn(g);
+  int bn = 256;
+  bool pair = false;
+  if (g.force_bn) {
+    bn = g.force_bn;
+    pair = g.force_pair == 2 && bn == 256;
+  } else {
+    choose_tile(g, &bn, &pair);
+  }
   switch (g.epilogue) {
-    case EPI_S8_BIAS_S8: return launch_bn<EPI_S8_BIAS_S8>(g, bn, stream);
-    case EPI_S8_BIAS_S8_RELU: return launch_bn<EPI_S8_BIAS_S8_RELU>(g, bn, stream);
-    case EPI_F32_BIAS_F32: return launch_bn<EPI_F32_BIAS_F32>(g, bn, stream);
-    case EPI_S32_BIAS_S32_ADD: return launch_bn<EPI_S32_BIAS_S32_ADD>(g, bn, stream);
-    case EPI_S32_BIAS_S32_SCALE: return launch_bn<EPI_S32_BIAS_S32_SCALE>(g, bn, stream);
-    case EPI_F32_ALPHA: return launch_bn<EPI_F32_ALPHA>(g, bn, stream);
-    case EPI_S8_ALPHA: return launch_bn<EPI_S8_ALPHA>(g, bn, stream);
-    case EPI_S32_RAW: return launch_bn<EPI_S32_RAW>(g, bn, stream);
+    case EPI_S8_BIAS_S8: return launch_bn<EPI_S8_BIAS_S8>(g, bn, pair, stream);
+    case EPI_S8_BIAS_S8_RELU: return launch_bn<EPI_S8_BIAS_S8_RELU>(g, bn, pair, stream);
+    case EPI_F32_BIAS_F32: return launch_bn<EPI_F32_BIAS_F32>(g, bn, pair, stream);
+    case EPI_S32_BIAS_S32_ADD: return launch_bn<EPI_S32_BIAS_S32_ADD>(g, bn, pair, stream);
+    case EPI_S32_BIAS_S32_SCALE: return launch_bn<EPI_S32_BIAS_S32_SCALE>(g, bn, pair, stream);
+    case EPI_F32_ALPHA: return launch_bn<EPI_F32_ALPHA>(g, bn, pair, stream);
+    case EPI_S8_ALPHA: return launch_bn<EPI_S8_ALPHA>(g, bn, pair, stream);
+    case EPI_S32_RAW: return launch_bn<EPI_S32_RAW>(g, bn, pair, stream);
   }
   set_error("unknown epilogue %d", g.epilogue);
   return TI_E_INVALID;

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the W8A8 kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, never multicast), tcgen05 (TMEM
+// mbarrier, TMA (cp.async.bulk.tensor, one CTA per load), tcgen05 (TMEM
 // allocation, UMMA issue/commit, TMEM loads) and the descriptor encodings.
 //
 // Every blocking wait in this file is bounded: a wait that exceeds
@@ -51,6 +51,26 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ------------------------------------------------------------------ cluster
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Address of the same shared-memory location in CTA `cta` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+  return r;
+}
+
+// Hardware barrier over all threads of all CTAs of the cluster (not a spin loop).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ----------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -65,16 +85,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Arrive on the barrier at the same smem offset in CTA `cta` of the cluster.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
-  asm volatile(
-      "{\n\t"
-      ".reg .b32 r;\n\t"
-      "mapa.shared::cluster.u32 r, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [r];\n\t"
-      "}\n" ::"r"(bar),
-      "r"(cta)
-      : "memory");
+// Arrive on a barrier given by its shared::cluster address (see mapa_shared).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
 }
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
@@ -159,6 +173,20 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint
       : "memory");
 }
 
+// 4-D tiled load issued by a CTA of a CTA pair: the data lands in this CTA's
+// shared memory, the completion bytes are counted on `cluster_bar`, which may
+// be a barrier of the peer CTA (shared::cluster address).  Each CTA loads its
+// own operand half.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void* tmap,
+                                                 uint32_t cluster_bar, int c0, int c1, int c2,
+                                                 int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 // --------------------------------------------------------------------- TMEM
 template <int kCtaGroup = 1>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -225,6 +253,17 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
+}
+
+// CTA-pair form: one barrier ARRIVE is delivered to the barrier at this
+// shared-memory offset in both CTAs of the pair (CTA mask 0b11) once all MMAs
+// issued so far have completed.  This signals barriers only; no data moves.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;" ::"r"(bar),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
 }
 
 // 32 lanes x 32 columns of 32-bit TMEM cells -> 32 registers per thread

@@ -62,7 +62,7 @@ class _GemmDesc(ctypes.Structure):
         ("strideA", _i64), ("strideB", _i64), ("strideC", _i64),
         ("stride2A", _i64), ("stride2B", _i64), ("stride2C", _i64),
         ("alpha", _f32), ("beta", _f32),
-        ("epilogue", ctypes.c_int32), ("tile_n", ctypes.c_int32),
+        ("epilogue", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
     ]
 
 
@@ -353,7 +353,7 @@ def softmax_q(scores, mask=None, num_heads=1, causal=-1):
 
 def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, lda, ldb, ldc,
                stride_a=0, stride_b=0, stride_c=0, stride2_a=0, stride2_b=0, stride2_c=0,
-               alpha=1.0, beta=0.0, tile_n=0):
+               alpha=1.0, beta=0.0, tile_n=0, cta_pair=0):
     """Strided form (ti_gemm_i8_ex): operands are addressed through explicit
     element strides starting at each tensor's data pointer, so views can be
     multiplied without contiguous copies.  Writes into `out` and returns it."""
@@ -386,7 +386,7 @@ def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, ld
     d.lda, d.ldb, d.ldc = lda, ldb, ldc
     d.strideA, d.strideB, d.strideC = stride_a, stride_b, stride_c
     d.stride2A, d.stride2B, d.stride2C = stride2_a, stride2_b, stride2_c
-    d.alpha, d.beta, d.epilogue, d.tile_n = float(alpha), float(beta), epilogue, tile_n
+    d.alpha, d.beta, d.epilogue, d.tile_n, d.cta_pair = float(alpha), float(beta), epilogue, tile_n, cta_pair
     with _on_device(a.device):
         rc = _c_gemm_ex(ctypes.byref(d), _stream_ptr(a.device))
     _check(rc)
