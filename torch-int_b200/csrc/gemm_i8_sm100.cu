@@ -51,6 +51,7 @@ struct KernelParams {
   long long total_tiles;
   float alpha, beta;
   int group_m;              // rasterisation: M tiles per column sweep
+  int a_b1, a_b2, b_b1, b_b2;  // 0 where an operand is broadcast over a batch index (stride 0), else 1
 };
 
 // PAIR = false: one CTA computes a 128 x BN tile (tcgen05 cta_group::1).
@@ -225,13 +226,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // to halve the throughput of the whole kernel.
             const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
             if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * C::STAGE_BYTES);
-            tma_load_4d_pair(smem_u32(sa), &tmap_a, fb, kb * BK, row_a, tc.b1, tc.b2);
-            tma_load_4d_pair(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, row_b, tc.b1, tc.b2);
+            tma_load_4d_pair(smem_u32(sa), &tmap_a, fb, kb * BK, row_a, tc.b1 * p.a_b1, tc.b2 * p.a_b2);
+            tma_load_4d_pair(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, row_b, tc.b1 * p.b_b1,
+                             tc.b2 * p.b_b2);
           } else {
             const uint32_t fb = smem_u32(&full_bar[stage]);
             mbar_expect_tx(fb, C::STAGE_BYTES);
-            tma_load_4d(smem_u32(sa), &tmap_a, fb, kb * BK, row_a, tc.b1, tc.b2);
-            tma_load_4d(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, row_b, tc.b1, tc.b2);
+            tma_load_4d(smem_u32(sa), &tmap_a, fb, kb * BK, row_a, tc.b1 * p.a_b1, tc.b2 * p.a_b2);
+            tma_load_4d(smem_u32(sa + C::A_BYTES), &tmap_b, fb, kb * BK, row_b, tc.b1 * p.b_b1, tc.b2 * p.b_b2);
           }
           if (++stage == C::STAGES) {
             stage = 0;
@@ -436,6 +438,16 @@ bool make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t K, int64_t ro
     set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
     return false;
   }
+  // A batch index with stride 0 (broadcast operand) becomes a dimension of extent 1;
+  // the kernel then always passes coordinate 0 for it.
+  if (stride == 0 || batch == 1) {
+    batch = 1;
+    stride = ld * rows;
+  }
+  if (stride2 == 0 || batch2 == 1) {
+    batch2 = 1;
+    stride2 = stride * batch;
+  }
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows),
                         static_cast<cuuint64_t>(batch), static_cast<cuuint64_t>(batch2)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(stride),
@@ -506,6 +518,10 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
   p.alpha = g.alpha;
   p.beta = g.beta;
   p.group_m = PAIR ? 8 : 16;
+  p.a_b1 = (g.strideA != 0 && g.batch > 1) ? 1 : 0;
+  p.a_b2 = (g.stride2A != 0 && g.batch2 > 1) ? 1 : 0;
+  p.b_b1 = (g.strideB != 0 && g.batch > 1) ? 1 : 0;
+  p.b_b2 = (g.stride2B != 0 && g.batch2 > 1) ? 1 : 0;
   const int sms = num_sms();
   const long long workers = PAIR ? sms / 2 : sms;  // CTAs, or CTA pairs
   const int grid = static_cast<int>(p.total_tiles < workers ? p.total_tiles : workers) * (PAIR ? 2 : 1);
