@@ -169,6 +169,155 @@ class GemmWorkload:
         return run, ops / 1e12, f"first {rows} of {HG[0]} rows of the headline GEMM (all of W)", O.num_threads()
 
 
+# ------------------------------------------------------------------------ Int8 OPT workloads
+OPT_WORKLOADS = {
+    # name: (architecture, batch, prefill length, decode steps)
+    "opt30b": ("opt-30b", 8, 512, 128),
+    "opt175b": ("opt-175b", 16, 1024, 128),
+    "opt13b": ("opt-13b", 4, 512, 128),
+    "opt1.3b": ("opt-1.3b", 8, 512, 32),
+}
+
+
+class OptWorkload:
+    metric = "int8_opt_prefill_tokens_per_s"
+    unit = "tokens/s"
+    dtype = "int8 x int8 -> int32 GEMM/BMM, fp32 epilogues and residual stream, fp16 embeddings and lm_head"
+    scaling = "strong"
+
+    def __init__(self, device, key, world, rank):
+        from torch_int import _CUDA as C
+        from torch_int.models.random_init import opt_config, random_int8_opt
+        from torch_int.models.tensor_parallel import TensorParallel
+        self.C = C
+        self.key = key
+        arch, self.batch, self.seq, self.decode_steps = OPT_WORKLOADS[key]
+        self.arch = arch
+        self.cfg = opt_config(arch)
+        self.world = world
+        self.name = f"int8_{arch}_prefill_b{self.batch}_s{self.seq}" + (f"_tp{world}" if world > 1 else "")
+        tp = TensorParallel.from_world() if world > 1 else TensorParallel.single()
+        self.tp = tp
+        self.model = random_int8_opt(self.cfg, seed=1234 + rank, device=device, tp=tp, param_dtype=torch.float16,
+                                     consistent=False)
+        g = torch.Generator().manual_seed(0)
+        self.ids_host = torch.randint(0, self.cfg.vocab_size, (self.batch, self.seq), generator=g).pin_memory()
+        self.next_host = torch.empty((self.batch,), dtype=torch.long).pin_memory()
+        self.ids = self.ids_host.to(device)
+        self.device = device
+        self.h2d = self.ids_host.numel() * 8
+        self.d2h = self.next_host.numel() * 8
+        c0 = C.launch_count
+        self.step()
+        self.launches_per_step = C.launch_count - c0
+        e, f, l = self.cfg.hidden_size, self.cfg.ffn_dim, self.cfg.num_hidden_layers
+        t = self.batch * self.seq
+        h, d = self.cfg.num_attention_heads, e // self.cfg.num_attention_heads
+        self.gemm_ops = l * 2.0 * t * (4.0 * e * e + 2.0 * e * f)
+        self.bmm_ops = l * 2.0 * 2.0 * self.batch * h * self.seq * self.seq * d
+        self.head_flops = 2.0 * t * e * self.cfg.vocab_size
+
+    def step(self):
+        return self.model(self.ids).logits
+
+    def step_e2e(self):
+        ids = self.ids_host.to(self.device, non_blocking=True)
+        logits = self.model(ids).logits
+        self.next_host.copy_(logits[:, -1, :].argmax(dim=-1), non_blocking=True)
+
+    def units(self, n_gpus):
+        return float(self.batch * self.seq)  # tokens per step over the whole job
+
+    def config(self, n_gpus):
+        return {"workload": self.name, "architecture": self.arch, "layers": self.cfg.num_hidden_layers,
+                "hidden": self.cfg.hidden_size, "heads": self.cfg.num_attention_heads, "ffn": self.cfg.ffn_dim,
+                "vocab": self.cfg.vocab_size, "batch": self.batch, "prefill_len": self.seq,
+                "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single GPU",
+                "weights": "random int8 uniform on [-127,127], analytic per-tensor scales x U(0.7,1.3)",
+                "logits": "all positions (fp16 lm_head)",
+                "l2": "per step the layers stream their int8 weights (>> 126 MB L2)"}
+
+    def roofline(self, ms, peaks):
+        """The dominant kernel is the W8A8 GEMM: time the layer's largest one (fc1) alone, live."""
+        e, f = self.cfg.hidden_size, self.cfg.ffn_dim
+        t = self.batch * self.seq
+        layer = self.model.model.decoder.layers[0]
+        x = torch.randint(-127, 128, (t, e), dtype=torch.int8, device=self.device)
+        fn = lambda: layer.fc1._op(x)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 20
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        gms = e0.elapsed_time(e1) / reps
+        ops = 2.0 * t * layer.local_ffn * e
+        achieved = ops / (gms * 1e-3) / 1e12
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        step_ops = (self.gemm_ops + self.bmm_ops) / self.world
+        return {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TOP/s",
+                "frac": round(achieved / peak, 4), "traffic": None,
+                "kernel": f"gemm_i8_kernel (fc1: {t} x {layer.local_ffn} x {e}, ReLU int8 epilogue)",
+                "kernel_ms": round(gms, 4),
+                "peak_source": f"2 x cuBLAS bf16 sustained of MEASURED_PEAKS.json ({peaks['source']}); "
+                               "sustained because the kernel runs inside a long step",
+                "step_int8_tops_per_gpu": round(step_ops / (ms * 1e-3) / 1e12, 1),
+                "step_frac_of_peak": round(step_ops / (ms * 1e-3) / 1e12 / peak, 4)}
+
+    def decode_rate(self, steps=None):
+        """Greedy decoding with the static int8 cache after the prefill: tokens/s over `steps` steps."""
+        steps = steps or self.decode_steps
+        cache = self.model.new_cache(self.batch, self.seq + steps + 1)
+        out = self.model(self.ids, past_key_values=cache, use_cache=True, last_token_only=True)
+        nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+        for _ in range(3):
+            out = self.model(nxt, past_key_values=cache, use_cache=True, last_token_only=True)
+            nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps - 3):
+            out = self.model(nxt, past_key_values=cache, use_cache=True, last_token_only=True)
+            nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (steps - 3)
+        wbytes = sum(b.numel() for n, b in self.model.named_buffers() if b.dtype == torch.int8)
+        return {"decode_tokens_per_s": round(self.batch / (ms * 1e-3), 1), "decode_ms_per_step": round(ms, 3),
+                "decode_steps_timed": steps - 3, "decode_weight_gb_per_s_per_gpu": round(wbytes / (ms * 1e-3) / 1e9, 1)}
+
+    def cpu_sample(self):
+        return opt_cpu_sample(self.arch, self.batch, self.seq)
+
+
+def opt_cpu_sample(arch, batch, seq, tokens=64):
+    """Bounded CPU sample: ONE decoder layer at the full dimensions of `arch` on `tokens`
+    tokens of one sequence, evaluated by the oracle; the rate is extrapolated to the
+    whole model as tokens / (layer time x layers) and labelled as such."""
+    from oracle import opt_model as OM
+    from oracle import w8a8 as O
+    from torch_int.models.opt import Int8OPTConfig
+    from torch_int.models.random_init import OPT_ARCHS, random_int8_opt
+    h, layers, heads, ffn = OPT_ARCHS[arch]
+    cfg = Int8OPTConfig(vocab_size=64, hidden_size=h, num_hidden_layers=1, ffn_dim=ffn, num_attention_heads=heads,
+                        max_position_embeddings=tokens + 2)
+    model = random_int8_opt(cfg, seed=5, device="cpu", consistent=False)
+    sd = {k: v.detach() for k, v in model.state_dict().items()}
+    g = torch.Generator().manual_seed(1)
+    hidden = torch.randn((1, tokens, h), generator=g)
+    mask = O.causal_mask(1, tokens, tokens)
+
+    def run():
+        return OM.decoder_layer(sd, "model.decoder.layers.0", hidden, mask, heads)
+    units = tokens / float(layers)  # tokens per (layer-time x layers)
+    return run, units, (f"one {arch} decoder layer at full dimensions on {tokens} tokens of one sequence, "
+                        f"extrapolated x{layers} layers (embeddings and lm_head not included)"), O.num_threads()
+
+
 def time_steps(fn, steps, warmup, world):
     import torch.distributed as dist
     for _ in range(warmup):
@@ -210,42 +359,53 @@ def cpu_baseline(wl, min_seconds=10.0, max_reps=50):
 
 def pick_workload(name, world):
     if name in (None, "auto"):
-        name = "gemm"
-    if name == "gemm":
-        return GemmWorkload
+        name = "opt30b" if world == 1 else "opt175b"
+    if name == "gemm" or name in OPT_WORKLOADS:
+        return name
     raise SystemExit(f"unknown workload {name}")
 
 
 def run_reference(args, world, rank):
-    """CPU arm: the reference semantics on the host cores (the oracle's C port)."""
+    """CPU arm: the reference semantics on the host cores (the oracle's C port; the reference
+    itself has no CPU implementation of its GEMM/BMM path and cannot be built without CUTLASS)."""
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    WL = pick_workload(args.workload, world)
-    wl = WL.__new__(WL)
-    # CPU-only construction of the sample
-    m, n, k = HG
-    g = torch.Generator().manual_seed(0)
-    wl.x_host = torch.randint(-127, 128, (128, k), generator=g, dtype=torch.int8)
-    g1 = torch.Generator().manual_seed(1)
-    wl.w = torch.randint(-127, 128, (n, k), generator=g1, dtype=torch.int8)
-    wl.b = torch.randint(-127, 128, (n,), generator=g1, dtype=torch.int8)
-    wl.alpha, wl.beta = 1e-4, 0.01
-    run, units, sample, cores = wl.cpu_sample()
+    key = pick_workload(args.workload, world)
+    if key == "gemm":
+        wl = GemmWorkload.__new__(GemmWorkload)
+        m, n, k = HG
+        g = torch.Generator().manual_seed(0)
+        wl.x_host = torch.randint(-127, 128, (128, k), generator=g, dtype=torch.int8)
+        g1 = torch.Generator().manual_seed(1)
+        wl.w = torch.randint(-127, 128, (n, k), generator=g1, dtype=torch.int8)
+        wl.b = torch.randint(-127, 128, (n,), generator=g1, dtype=torch.int8)
+        wl.alpha, wl.beta = 1e-4, 0.01
+        run, units, sample, cores = wl.cpu_sample()
+        metric, unit, dtype, scaling, name = (GemmWorkload.metric, GemmWorkload.unit, GemmWorkload.dtype,
+                                              GemmWorkload.scaling, GemmWorkload.name)
+        config = {"workload": name, "M": HG[0], "N": HG[1], "K": HG[2], "sample": sample}
+    else:
+        arch, batch, seq, _ = OPT_WORKLOADS[key]
+        run, units, sample, cores = opt_cpu_sample(arch, batch, seq)
+        metric, unit, dtype, scaling = OptWorkload.metric, OptWorkload.unit, OptWorkload.dtype, OptWorkload.scaling
+        name = f"int8_{arch}_prefill_b{batch}_s{seq}" + (f"_tp{world}" if world > 1 else "")
+        config = {"workload": name, "architecture": arch, "batch": batch, "prefill_len": seq, "sample": sample}
     for _ in range(max(1, min(args.warmup, 2))):
         run()
+    steps = max(1, min(args.steps, 20))
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         run()
     dt = time.perf_counter() - t0
-    value = units * args.steps / dt
-    line = {"impl": "reference", "metric": WL.metric, "value": round(value, 4), "unit": WL.unit,
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(dt / args.steps * 1e3, 3), "higher_is_better": True, "scaling": WL.scaling,
-            "vs_baseline": None, "dtype": WL.dtype, "data": "synthetic (seeded uniform int8 on [-127,127])",
-            "config": {"workload": WL.name, "M": HG[0], "N": HG[1], "K": HG[2], "sample": sample},
-            "cpu_baseline": {"value": round(value, 4), "unit": WL.unit, "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": round(value, 4), "unit": WL.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    value = units * steps / dt
+    line = {"impl": "reference", "metric": metric, "value": round(value, 4), "unit": unit,
+            "n_gpus": world, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": round(dt / steps * 1e3, 3), "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": dtype, "data": "synthetic (seeded random int8 weights and inputs)",
+            "config": config,
+            "cpu_baseline": {"value": round(value, 4), "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": round(value, 4), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
@@ -253,15 +413,21 @@ def run_reference(args, world, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode-rate measurement of the OPT workloads")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for ncu: no end-to-end leg, no CPU baseline")
     args = ap.parse_args()
     world, rank, local = dist_env()
+    key = pick_workload(args.workload, world)
+    if args.steps is None:
+        args.steps = 1000 if key == "gemm" else 10
+    if args.warmup is None:
+        args.warmup = 5 if key == "gemm" else 3
     if args.impl == "reference":
         run_reference(args, world, rank)
         return
@@ -273,8 +439,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    WL = pick_workload(args.workload, world)
-    wl = WL(device)
+    wl = GemmWorkload(device) if key == "gemm" else OptWorkload(device, key, world, rank)
     peaks = measured_peaks()
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -283,6 +448,9 @@ def main():
     ms = time_steps(wl.step, args.steps, args.warmup, world)
     clocks = sampler.stop() if sampler else None
     ms_e2e = ms if args.profile else time_steps(wl.step_e2e, args.steps, args.warmup, world)
+    extra = {}
+    if key != "gemm" and not args.profile and not args.no_decode:
+        extra = wl.decode_rate()
     from torch_int import _CUDA as C
     status = C.device_status()
     assert status == 0, f"a kernel reported wait timeout {status}"
@@ -291,7 +459,7 @@ def main():
         line = {"metric": wl.metric, "value": round(units / (ms * 1e-3), 2), "unit": wl.unit, "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
                 "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
-                "data": "synthetic (seeded uniform int8 on [-127,127])", "config": wl.config(world),
+                "data": "synthetic (seeded random int8 weights and inputs)", "config": wl.config(world),
                 "e2e": {"value": round(units / (ms_e2e * 1e-3), 2), "unit": wl.unit,
                         "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                         "ms_per_step": round(ms_e2e, 4)},
@@ -299,6 +467,7 @@ def main():
                 "roofline": wl.roofline(ms, peaks)}
         if world == 1 and not args.no_cpu_baseline and not args.profile:
             line["cpu_baseline"] = cpu_baseline(wl)
+        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

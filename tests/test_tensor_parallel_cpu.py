@@ -1,0 +1,127 @@
+"""Tensor-parallel host logic on CPU ranks (gloo, world size 2 and 4): the weight
+sharder and the int32 all-reduce wrapper of the product, with the per-rank
+arithmetic done by the oracle.  The sharded evaluation must equal the unsharded
+oracle bit for bit, because the exchanged partial sums are integers."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import opt_model as OM
+from oracle import w8a8 as O
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _model_sd(hidden=128, heads=4, ffn=256, layers=1, seed=3):
+    from torch_int.models.opt import Int8OPTConfig
+    from torch_int.models.random_init import random_int8_opt
+    cfg = Int8OPTConfig(vocab_size=64, hidden_size=hidden, num_hidden_layers=layers, ffn_dim=ffn,
+                        num_attention_heads=heads, max_position_embeddings=64)
+    model = random_int8_opt(cfg, seed=seed, device="cpu")
+    return cfg, {k: v.detach() for k, v in model.state_dict().items()}
+
+
+def _rank_main(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torch_int.models.tensor_parallel import TensorParallel
+        torch.set_num_threads(1)
+        tp = TensorParallel.from_world()
+        assert (tp.size, tp.rank) == (world, rank)
+        cfg, full = _model_sd()
+        sd = tp.shard_state_dict(full)
+        e, heads = cfg.hidden_size, cfg.num_attention_heads
+        hl, d = heads // world, e // heads
+        p = "model.decoder.layers.0"
+        assert sd[p + ".self_attn.q_proj.weight"].shape == (e // world, e)
+        assert sd[p + ".self_attn.q_proj.bias"].shape == (1, e // world)
+        assert sd[p + ".self_attn.out_proj.weight"].shape == (e, e // world)
+        assert sd[p + ".self_attn.out_proj.bias"].shape == (1, e)
+        assert sd[p + ".fc1.weight"].shape == (cfg.ffn_dim // world, e)
+        assert sd[p + ".fc2.weight"].shape == (e, cfg.ffn_dim // world)
+        g = torch.Generator().manual_seed(11)
+        hidden = torch.randn((2, 16, e), generator=g)
+        mask = O.causal_mask(2, 16, 16)
+        bsz, tgt = 2, 16
+        # --- this rank's part of the layer, with the product's all-reduce in the two exchange steps
+        residual = hidden.clone()
+        h8 = O.layernorm_q(residual, sd[p + ".self_attn_layer_norm.weight"], sd[p + ".self_attn_layer_norm.bias"], 1e-5)
+        x2d = h8.view(-1, e)
+
+        def shape(t):
+            return t.view(bsz, tgt, hl, d).transpose(1, 2).reshape(bsz * hl, tgt, d).contiguous()
+
+        a = p + ".self_attn"
+        q, k, v = (shape(OM._linear_s8(sd, f"{a}.{n}", x2d)) for n in ("q_proj", "k_proj", "v_proj"))
+        probs = O.softmax_q(O.bmm_s8t_s8n_f32t(q, k, float(sd[a + ".qk_bmm.a"])), mask)
+        ctx = O.bmm_s8t_s8n_s8t(probs, v.transpose(1, 2).contiguous(), float(sd[a + ".pv_bmm.a"]))
+        ctx = ctx.view(bsz, hl, tgt, d).transpose(1, 2).reshape(bsz * tgt, hl * d).contiguous()
+        part = tp.all_reduce_int32(OM.row_parallel_partial(ctx, sd[a + ".out_proj.weight"]))
+        residual, h8 = O.dq_add_layernorm_q_bias(part.view(bsz, tgt, e), float(sd[a + ".out_proj.a"]),
+                                                 sd[a + ".out_proj.bias"].reshape(-1), residual,
+                                                 sd[p + ".final_layer_norm.weight"], sd[p + ".final_layer_norm.bias"], 1e-5)
+        f8 = OM._linear_s8(sd, p + ".fc1", h8.view(-1, e), relu=True)
+        part = tp.all_reduce_int32(OM.row_parallel_partial(f8, sd[p + ".fc2.weight"]))
+        residual, _ = O.dq_add_layernorm_q_bias(part.view(bsz, tgt, e), float(sd[p + ".fc2.a"]),
+                                                sd[p + ".fc2.bias"].reshape(-1), residual,
+                                                torch.ones(e), torch.zeros(e), 1e-5)
+        want, _ = OM.decoder_layer(full, p, hidden, mask, heads)
+        ok = torch.equal(residual, want)
+        # a float tensor must be refused: the exchange is defined on int32 partial sums only
+        refused = False
+        try:
+            tp.all_reduce_int32(torch.zeros(4))
+        except RuntimeError:
+            refused = True
+        ret[rank] = (ok, refused, float((residual - want).abs().max()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_layer_equals_unsharded(world):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, ret)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=240)
+        assert pr.exitcode == 0, f"rank exited with {pr.exitcode}"
+    for r in range(world):
+        ok, refused, err = ret[r]
+        assert ok, f"rank {r}: sharded result differs from the unsharded oracle (max |d| = {err})"
+        assert refused
+
+
+def test_oracle_tp_restatement_matches():
+    cfg, full = _model_sd(hidden=128, heads=4, ffn=256)
+    from torch_int.models.tensor_parallel import TensorParallel
+    g = torch.Generator().manual_seed(12)
+    hidden = torch.randn((1, 32, 128), generator=g)
+    mask = O.causal_mask(1, 32, 32)
+    want, _ = OM.decoder_layer(full, "model.decoder.layers.0", hidden, mask, 4)
+    for world in (1, 2, 4):
+        shards = [TensorParallel(world, r).shard_state_dict(full) for r in range(world)]
+        got = OM.decoder_layer_tp(shards, "model.decoder.layers.0", hidden, mask, 4)
+        assert torch.equal(got, want), f"tp={world}"
+
+
+def test_single_rank_context_is_a_no_op():
+    from torch_int.models.tensor_parallel import TensorParallel
+    tp = TensorParallel.single()
+    t = torch.arange(6, dtype=torch.int32)
+    assert tp.all_reduce_int32(t) is t
+    sd = {"x.q_proj.weight": torch.zeros(4, 4)}
+    assert tp.shard_state_dict(sd)["x.q_proj.weight"].shape == (4, 4)

@@ -110,9 +110,14 @@ _EPI_BIAS_DTYPE = {
 }
 
 
+launch_count = 0  # kernels of this library enqueued through this module since import
+
+
 def _check(rc):
+    global launch_count
     if rc != 0:
         raise RuntimeError("torch_int._CUDA: " + _c_last_error().decode("utf-8", "replace"))
+    launch_count += 1
 
 
 def _stream_ptr(device):
