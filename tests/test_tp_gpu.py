@@ -1,0 +1,65 @@
+"""Tensor-parallel Int8 OPT on real GPUs (NCCL): the logits of a tp=2 (and tp=4) run must be
+bit-identical to the single-GPU run of the same model, because only int32 partial sums are
+exchanged.  Needs at least 2 GPUs; skipped otherwise."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from torch_int import _CUDA as C
+        from torch_int.models.opt import Int8OPTConfig
+        from torch_int.models.random_init import random_int8_opt
+        from torch_int.models.tensor_parallel import TensorParallel
+        cfg = Int8OPTConfig(vocab_size=512, hidden_size=512, num_hidden_layers=3, ffn_dim=2048,
+                            num_attention_heads=8, max_position_embeddings=256)
+        dev = torch.device("cuda", rank)
+        tp_model = random_int8_opt(cfg, seed=21, device=dev, tp=TensorParallel.from_world(), consistent=True)
+        g = torch.Generator().manual_seed(5)
+        ids = torch.randint(0, cfg.vocab_size, (2, 77), generator=g).to(dev)
+        logits = tp_model(ids).logits
+        gen = tp_model.generate_greedy(ids[:, :20], 5)
+        ok = True
+        if rank == 0:
+            one = random_int8_opt(cfg, seed=21, device=dev, tp=TensorParallel.single(), consistent=True)
+            want = one(ids).logits
+            ok = torch.equal(logits, want) and torch.equal(gen, one.generate_greedy(ids[:, :20], 5))
+        ret[rank] = (ok, C.device_status())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_logits_equal_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    for r in range(world):
+        ok, status = ret[r]
+        assert ok and status == 0, f"rank {r}: equal={ok} status={status}"
