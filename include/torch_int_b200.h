@@ -160,6 +160,13 @@ int ti_softmax_q(const float* scores, const float* mask, int8_t* probs, int64_t 
                  int64_t heads, int64_t T, int64_t S, int64_t lds, int64_t ldp, int causal,
                  void* stream);
 
+/* int8 values v [B, T, H, D] (what v_proj produces) -> vt [B, H, D, ld_out], written at columns
+ * [col0, col0 + T): the transposed, K-major operand of the P.V product.
+ * Replaces value_states.transpose(1, 2).contiguous() (torch_int/models/opt.py:180) and lets a
+ * pre-allocated cache be filled in place. */
+int ti_transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
+                        int64_t ld_out, int64_t col0, void* stream);
+
 /* ---- status ---- */
 
 /* Message of the last error raised on the calling thread ("" if none). */

@@ -85,7 +85,7 @@ def test_dq_add_module(cuda_ops):
 
 
 @pytest.mark.parametrize("bsz,heads,t,s", [(1, 1, 1, 16), (2, 3, 16, 16), (2, 4, 48, 112), (1, 5, 512, 512),
-                                           (1, 2, 16, 2048), (2, 2, 1, 528)])
+                                           (1, 2, 16, 2048), (2, 2, 1, 528), (1, 1, 3, 2064), (1, 3, 40, 1040)])
 def test_softmax_q(cuda_ops, bsz, heads, t, s):
     scores = randn((bsz * heads, t, s), 9, 2.5)
     mask = O.causal_mask(bsz, t, s)
@@ -97,3 +97,15 @@ def test_softmax_q(cuda_ops, bsz, heads, t, s):
     pad = mask.clone()
     pad[:, :, :, : s // 4] = torch.finfo(torch.float32).min
     assert_quant_close(cuda_ops.softmax_q(scores.cuda(), pad.cuda(), heads), O.softmax_q(scores, pad), 0.999, "padding")
+
+
+@pytest.mark.parametrize("b,t,h,d,cap,col0", [(2, 48, 3, 128, 64, 16), (1, 1, 5, 64, 32, 7), (3, 130, 2, 128, 144, 0),
+                                              (2, 512, 4, 128, 512, 0)])
+def test_transpose_values(cuda_ops, b, t, h, d, cap, col0):
+    g = torch.Generator().manual_seed(10)
+    v = torch.randint(-128, 128, (b, t, h, d), generator=g, dtype=torch.int8)
+    vt = torch.full((b, h, d, cap), 77, dtype=torch.int8, device="cuda")
+    cuda_ops.transpose_values(v.cuda(), vt, col0)
+    want = torch.full((b, h, d, cap), 77, dtype=torch.int8)
+    want[..., col0:col0 + t] = v.permute(0, 2, 3, 1)   # value_states.transpose(1, 2) of opt.py:180
+    assert torch.equal(vt.cpu(), want)

@@ -183,6 +183,11 @@ int ti_softmax_q(const float* scores, const float* mask, int8_t* probs, int64_t 
                    static_cast<cudaStream_t>(stream));
 }
 
+int ti_transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
+                        int64_t ld_out, int64_t col0, void* stream) {
+  return transpose_values(v, vt, B, T, H, D, ld_out, col0, static_cast<cudaStream_t>(stream));
+}
+
 const char* ti_last_error(void) { return last_error(); }
 
 int ti_device_status(int* status, int reset) {

@@ -316,6 +316,119 @@ softmax_q_kernel(const float* __restrict__ scores, const float* __restrict__ mas
   }
 }
 
+// Warp-per-row form of softmax_q for rows of up to 32 * 4 * VPT floats: eight
+// rows per CTA, no block-wide barrier, VPT independent 16-byte loads in flight
+// per lane.  With a generated causal mask, chunks that lie entirely behind the
+// diagonal are not read at all: their probability is exactly zero (the
+// reference adds FLT_LOWEST to them, exp() of which underflows to 0).
+template <int VPT>
+__global__ void __launch_bounds__(256)
+softmax_q_warp_kernel(const float* __restrict__ scores, const float* __restrict__ mask,
+                      int8_t* __restrict__ out, long long rows, int T, int S, int heads,
+                      long long lds, long long ldo, int causal) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int t = static_cast<int>(row % T);
+  const long long bh = row / T;
+  const float* sr = scores + row * lds;
+  const float* mr = mask ? mask + ((bh / heads) * T + t) * static_cast<long long>(S) : nullptr;
+  const int s4 = S >> 2;
+  const int lim = (mr == nullptr && causal >= 0) ? t + causal : 0x7fffffff;  // last visible column
+  float4 v[VPT];
+  float mx = -FLT_MAX;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = lane + j * 32;
+    if (i < s4 && 4 * i <= lim) {
+      float4 a = *reinterpret_cast<const float4*>(sr + 4 * i);
+      if (mr) {
+        const float4 m = *reinterpret_cast<const float4*>(mr + 4 * i);
+        a.x += m.x; a.y += m.y; a.z += m.z; a.w += m.w;
+      } else {
+        if (4 * i + 1 > lim) a.y += -FLT_MAX;
+        if (4 * i + 2 > lim) a.z += -FLT_MAX;
+        if (4 * i + 3 > lim) a.w += -FLT_MAX;
+      }
+      a.x = fmaxf(a.x, -FLT_MAX); a.y = fmaxf(a.y, -FLT_MAX);
+      a.z = fmaxf(a.z, -FLT_MAX); a.w = fmaxf(a.w, -FLT_MAX);
+      v[j] = a;
+      mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+    }
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = lane + j * 32;
+    if (i < s4 && 4 * i <= lim) {
+      v[j].x = expf(v[j].x - mx); v[j].y = expf(v[j].y - mx);
+      v[j].z = expf(v[j].z - mx); v[j].w = expf(v[j].w - mx);
+      sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+  }
+  sum = warp_sum(sum);
+  int8_t* orow = out + row * ldo;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = lane + j * 32;
+    if (i < s4) {
+      uint32_t packed = 0;
+      if (4 * i <= lim) {
+        const float p0 = __fdiv_rn(v[j].x, sum) * 127.f, p1 = __fdiv_rn(v[j].y, sum) * 127.f;
+        const float p2 = __fdiv_rn(v[j].z, sum) * 127.f, p3 = __fdiv_rn(v[j].w, sum) * 127.f;
+        packed = pack_s8x4(p0, p1, p2, p3);
+      }
+      *reinterpret_cast<uint32_t*>(orow + 4 * i) = packed;
+    }
+  }
+}
+
+// int8 [B, T, H, D] -> [B, H, D, ld_out] at column offset col0 (the transposed,
+// K-major value layout P.V needs).  64 x 64 byte tiles through shared memory,
+// 4-byte accesses on both sides.
+__global__ void __launch_bounds__(256)
+transpose_values_kernel(const int8_t* __restrict__ v, int8_t* __restrict__ vt, int T, int H, int D,
+                        long long ld_out, int col0) {
+  __shared__ int8_t tile[64][64 + 4];
+  const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const int bh = blockIdx.z, b = bh / H, h = bh % H;
+  const int8_t* src = v + ((static_cast<long long>(b) * T) * H + h) * D;  // row t at + t*H*D
+  // load: 64 rows (t) x 64 bytes (d); thread -> (row = tid/16 + 16*i, 4-byte column = tid%16)
+  const int c4 = threadIdx.x & 15, r = threadIdx.x >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = t0 + r + 16 * i;
+    uint32_t w = 0;
+    if (t < T && d0 + 4 * c4 < D)
+      w = *reinterpret_cast<const uint32_t*>(src + static_cast<long long>(t) * H * D + d0 + 4 * c4);
+    *reinterpret_cast<uint32_t*>(&tile[r + 16 * i][4 * c4]) = w;
+  }
+  __syncthreads();
+  // store: 64 rows (d) x 64 bytes (t)
+  int8_t* dst = vt + (static_cast<long long>(bh) * D) * ld_out + col0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = r + 16 * i;
+    const int tt = 4 * c4;
+    if (d0 + d < D) {
+      int8_t* p = dst + static_cast<long long>(d0 + d) * ld_out + t0 + tt;
+      const int8_t e0 = tile[tt][d], e1 = tile[tt + 1][d], e2 = tile[tt + 2][d], e3 = tile[tt + 3][d];
+      if (t0 + tt + 3 < T && ((reinterpret_cast<uintptr_t>(p) & 3) == 0)) {
+        *reinterpret_cast<uint32_t*>(p) = (static_cast<uint32_t>(static_cast<uint8_t>(e0))) |
+                                          (static_cast<uint32_t>(static_cast<uint8_t>(e1)) << 8) |
+                                          (static_cast<uint32_t>(static_cast<uint8_t>(e2)) << 16) |
+                                          (static_cast<uint32_t>(static_cast<uint8_t>(e3)) << 24);
+      } else {
+        if (t0 + tt < T) p[0] = e0;
+        if (t0 + tt + 1 < T) p[1] = e1;
+        if (t0 + tt + 2 < T) p[2] = e2;
+        if (t0 + tt + 3 < T) p[3] = e3;
+      }
+    }
+  }
+}
+
 template <typename F>
 int check_launch(const char* name, F&& f) {
   f();
@@ -467,6 +580,24 @@ int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch
     set_error("softmax_q: S=%lld exceeds the supported maximum of %d", (long long)S, 256 * kMaxVpt * 4);
     return TI_E_INVALID;
   }
+  if (s4 <= 32 * 16) {
+    const unsigned wgrid = static_cast<unsigned>((rows + 7) / 8);
+    const int wv = (s4 + 31) / 32;
+    int rc = TI_OK;
+#define TI_SOFTMAX_WARP(V)                                                                          \
+  rc = check_launch("softmax_q_warp", [&] {                                                         \
+    softmax_q_warp_kernel<V><<<wgrid, 256, 0, stream>>>(scores, mask, out, rows, static_cast<int>(T), \
+                                                        static_cast<int>(S), static_cast<int>(heads), \
+                                                        lds, ldo, causal);                          \
+  })
+    if (wv <= 1) TI_SOFTMAX_WARP(1);
+    else if (wv <= 2) TI_SOFTMAX_WARP(2);
+    else if (wv <= 4) TI_SOFTMAX_WARP(4);
+    else if (wv <= 8) TI_SOFTMAX_WARP(8);
+    else TI_SOFTMAX_WARP(16);
+#undef TI_SOFTMAX_WARP
+    return rc;
+  }
   const unsigned grid = static_cast<unsigned>(rows);
   if (s4 <= 128)
     return check_launch("softmax_q", [&] {
@@ -482,6 +613,30 @@ int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch
                       static_cast<int>(heads), lds, ldo, causal);
                 }));
   return rc;
+}
+
+int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
+                     int64_t ld_out, int64_t col0, cudaStream_t stream) {
+  if (B < 0 || T < 0 || H <= 0 || D <= 0 || ld_out < col0 + T || col0 < 0) {
+    set_error("transpose_values: bad shape");
+    return TI_E_INVALID;
+  }
+  if (B == 0 || T == 0) return TI_OK;
+  if (!v || !vt) {
+    set_error("transpose_values: null pointer");
+    return TI_E_INVALID;
+  }
+  if (D % 4 != 0 || (reinterpret_cast<uintptr_t>(v) & 3) != 0 || B * H > 65535) {
+    set_error("transpose_values: head_dim must be a multiple of 4, the input 4-byte aligned and "
+              "batch*heads <= 65535");
+    return TI_E_INVALID;
+  }
+  dim3 grid(static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>((D + 63) / 64),
+            static_cast<unsigned>(B * H));
+  return check_launch("transpose_values", [&] {
+    transpose_values_kernel<<<grid, 256, 0, stream>>>(v, vt, static_cast<int>(T), static_cast<int>(H),
+                                                      static_cast<int>(D), ld_out, static_cast<int>(col0));
+  });
 }
 
 }  // namespace ti

@@ -21,4 +21,8 @@ int dq_add_layernorm_q(const int32_t* in, float scale, const void* res, int res_
 int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch_heads, int64_t heads,
               int64_t T, int64_t S, int64_t lds, int64_t ldo, int causal, cudaStream_t stream);
 
+// int8 v [B, T, H, D] -> vt [B, H, D, ld_out], written at columns [col0, col0 + T).
+int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
+                     int64_t ld_out, int64_t col0, cudaStream_t stream);
+
 }  // namespace ti

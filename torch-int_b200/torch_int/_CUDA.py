@@ -29,7 +29,7 @@ __all__ = [
     "linear_a8_w8_b32_o32", "linear_a8_w8_b32_o32_with_scaling",
     "bmm_s8t_s8n_s8t", "bmm_s8t_s8n_f32t", "bmm_s8t_s8n_s32t", "dq_add_layernorm_q",
     # extras
-    "layernorm_q", "softmax_q", "dq_add_layernorm_q_bias", "gemm_i8_ex", "device_status",
+    "layernorm_q", "softmax_q", "dq_add_layernorm_q_bias", "gemm_i8_ex", "transpose_values", "device_status",
     "library_path",
 ]
 
@@ -90,6 +90,7 @@ _c_dq_add_ln_q_bias = _sig("ti_dq_add_layernorm_q_bias",
                            [_ptr, _f32, _ptr, _ptr, _i32, _ptr, _ptr, _f32, _ptr, _ptr, _i64, _i64, _ptr])
 _c_ln_q = _sig("ti_layernorm_q", [_ptr, _i32, _ptr, _ptr, _f32, _ptr, _i64, _i64, _ptr])
 _c_softmax_q = _sig("ti_softmax_q", [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _ptr])
+_c_transpose_values = _sig("ti_transpose_values", [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr])
 _c_last_error = _sig("ti_last_error", [], ctypes.c_char_p)
 _c_device_status = _sig("ti_device_status", [ctypes.POINTER(ctypes.c_int), _i32])
 _c_abi_version = _sig("ti_abi_version", [])
@@ -396,6 +397,20 @@ def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, ld
         rc = _c_gemm_ex(ctypes.byref(d), _stream_ptr(a.device))
     _check(rc)
     return out
+
+
+def transpose_values(v, vt, col0=0):
+    """int8 v [B, T, H, D] -> vt [B, H, D, cap] at columns [col0, col0 + T): the transposed
+    value layout P.V consumes.  Replaces transpose(1, 2).contiguous() of torch_int/models/opt.py:180."""
+    _require(v, "v", torch.int8, 4)
+    _require(vt, "vt", torch.int8, 4)
+    b, t, h, d = v.shape
+    if vt.shape[:3] != (b, h, d) or vt.shape[3] < col0 + t or vt.device != v.device:
+        raise RuntimeError(f"vt {tuple(vt.shape)} cannot hold v {tuple(v.shape)} at column {col0}")
+    with _on_device(v.device):
+        rc = _c_transpose_values(v.data_ptr(), vt.data_ptr(), b, t, h, d, vt.shape[3], col0, _stream_ptr(v.device))
+    _check(rc)
+    return vt
 
 
 def device_status(reset=True):

@@ -48,5 +48,5 @@ class StaticInt8KVCache:
                          batch=bsz, lda=e, ldb=e, ldc=el, stride_a=tgt_len * e, stride_b=0,
                          stride_c=self.capacity * el, alpha=k_proj._scalar("a"), beta=k_proj._scalar("b"))
         v = v_proj._op(x2d)
-        vt[:, :, :, past_len:past_len + tgt_len] = v.view(bsz, tgt_len, self.local_heads, self.head_dim).permute(0, 2, 3, 1)
+        C.transpose_values(v.view(bsz, tgt_len, self.local_heads, self.head_dim), vt, past_len)
         return kc, vt

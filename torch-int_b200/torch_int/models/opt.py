@@ -164,8 +164,9 @@ class Int8OPTAttention(nn.Module):
                 kp = torch.zeros((bsz, src_pad, el), dtype=torch.int8, device=k.device)
                 kp[:, :src_len] = k.view(bsz, tgt_len, el)
                 k_rows, k_batch_stride = kp, src_pad * el
-            vt = torch.zeros((bsz, hl, d, src_pad), dtype=torch.int8, device=v.device)
-            vt[..., :src_len] = v.view(bsz, tgt_len, hl, d).permute(0, 2, 3, 1)
+            vt = (torch.zeros if src_pad != src_len else torch.empty)((bsz, hl, d, src_pad), dtype=torch.int8,
+                                                                      device=v.device)
+            C.transpose_values(v.view(bsz, tgt_len, hl, d), vt, 0)
             vt_row_stride = src_pad
         causal = past_len if mask is None else -1
         ctx = self.attention_core(q.view(bsz, tgt_len, el), k_rows, vt, bsz, tgt_len, src_len, src_pad,
