@@ -33,15 +33,18 @@ def _rank_main(rank, world, port, ret):
                             num_attention_heads=8, max_position_embeddings=256)
         dev = torch.device("cuda", rank)
         tp_model = random_int8_opt(cfg, seed=21, device=dev, tp=TensorParallel.from_world(), consistent=True)
+        tp_model.model.decoder.tp.min_pipeline_tokens = 32  # exercise the pipelined loop at test sizes
         g = torch.Generator().manual_seed(5)
         ids = torch.randint(0, cfg.vocab_size, (2, 77), generator=g).to(dev)
-        logits = tp_model(ids).logits
-        gen = tp_model.generate_greedy(ids[:, :20], 5)
+        logits = tp_model(ids).logits                       # one group of sequences
+        ids4 = torch.randint(0, cfg.vocab_size, (4, 48), generator=g).to(dev)
+        logits4 = tp_model(ids4).logits                     # several groups: pipelined exchanges
+        gen = tp_model.generate_greedy(ids[:, :20], 5)      # static cache, one-token steps
         ok = True
         if rank == 0:
             one = random_int8_opt(cfg, seed=21, device=dev, tp=TensorParallel.single(), consistent=True)
-            want = one(ids).logits
-            ok = torch.equal(logits, want) and torch.equal(gen, one.generate_greedy(ids[:, :20], 5))
+            ok = (torch.equal(logits, one(ids).logits) and torch.equal(logits4, one(ids4).logits)
+                  and torch.equal(gen, one.generate_greedy(ids[:, :20], 5)))
         ret[rank] = (ok, C.device_status())
     finally:
         dist.destroy_process_group()

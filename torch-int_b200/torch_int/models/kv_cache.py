@@ -29,14 +29,16 @@ class StaticInt8KVCache:
     def reset(self):
         self.length = 0
 
-    def append(self, layer_idx, k_proj, v_proj, x2d, bsz, tgt_len, past_len):
+    def append(self, layer_idx, k_proj, v_proj, x2d, bsz, tgt_len, past_len, b0=0):
         """Projects x2d [B*T, E] to keys and values and stores them at positions
-        [past_len, past_len + T).  The key GEMM writes straight into the cache."""
-        if bsz != self.batch_size:
-            raise RuntimeError(f"cache was allocated for batch {self.batch_size}, got {bsz}")
+        [past_len, past_len + T) of the sequences [b0, b0 + B).  The key GEMM writes
+        straight into the cache.  Returns the (keys, transposed values) views of
+        those sequences."""
+        if b0 < 0 or b0 + bsz > self.batch_size:
+            raise RuntimeError(f"cache was allocated for batch {self.batch_size}, got sequences [{b0}, {b0 + bsz})")
         if past_len + tgt_len > self.capacity:
             raise RuntimeError(f"cache capacity {self.capacity} exceeded ({past_len} + {tgt_len})")
-        kc, vt = self.keys[layer_idx], self.values_t[layer_idx]
+        kc, vt = self.keys[layer_idx][b0:b0 + bsz], self.values_t[layer_idx][b0:b0 + bsz]
         el, e = kc.shape[2], x2d.shape[1]
         dst = kc[:, past_len:, :]  # view starting at the first new row of batch 0
         if tgt_len == 1:

@@ -144,9 +144,10 @@ class Int8OPTAttention(nn.Module):
 
     @torch.no_grad()
     def forward_fused(self, hidden_int8, cache: Optional[StaticInt8KVCache], layer_idx: int, past_len: int,
-                      mask: Optional[torch.Tensor]):
+                      mask: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, b0: int = 0):
         """int8 [B,T,E] -> int32 partial sums of out_proj [B*T, E] (this rank's input
-        slice; bias and scale are applied after the all-reduce)."""
+        slice; bias and scale are applied after the reduction over the ranks).  `out`:
+        optional destination; `b0`: index of the first of these sequences in the cache."""
         bsz, tgt_len, _ = hidden_int8.shape
         hl, d, el = self.local_heads, self.head_dim, self.local_dim
         x2d = hidden_int8.view(-1, self.embed_dim)
@@ -154,7 +155,7 @@ class Int8OPTAttention(nn.Module):
         src_len = past_len + tgt_len
         src_pad = _round_up(src_len, 16)
         if cache is not None:
-            k_rows, vt = cache.append(layer_idx, self.k_proj, self.v_proj, x2d, bsz, tgt_len, past_len)
+            k_rows, vt = cache.append(layer_idx, self.k_proj, self.v_proj, x2d, bsz, tgt_len, past_len, b0)
             k_row_stride, k_batch_stride, vt_row_stride = el, cache.capacity * el, cache.capacity
         else:
             k = self.k_proj._op(x2d)
@@ -172,7 +173,8 @@ class Int8OPTAttention(nn.Module):
         ctx = self.attention_core(q.view(bsz, tgt_len, el), k_rows, vt, bsz, tgt_len, src_len, src_pad,
                                   k_row_stride, k_batch_stride, vt_row_stride, causal, mask)
         ctx2d = ctx.view(-1, el)
-        acc = torch.empty((ctx2d.shape[0], self.embed_dim), dtype=torch.int32, device=ctx.device)
+        acc = out if out is not None else torch.empty((ctx2d.shape[0], self.embed_dim), dtype=torch.int32,
+                                                      device=ctx.device)
         C.gemm_i8_ex(ctx2d, self.out_proj.weight, acc, epilogue=C.EPI_S32_RAW, m=ctx2d.shape[0],
                      n=self.embed_dim, k=el, lda=el, ldb=el, ldc=self.embed_dim)
         return acc
@@ -426,6 +428,69 @@ class Int8OPTDecoder(nn.Module):
         mask = torch.full((bsz, 1, tgt_len, src_pad), neg, dtype=dtype, device=dev)
         return mask.masked_fill(visible, 0.0).contiguous()
 
+    def _layers_pipelined(self, residual, cache, past_len, mask, chunks):
+        """Tensor-parallel layer loop.  The batch is cut into `chunks` groups of whole
+        sequences; per group and per exchange point the int32 partial sums are
+        reduce-scattered over the ranks by token rows, the fused dequant + bias +
+        residual add + LayerNorm-quantise runs on this rank's rows only (the residual
+        stream stays sharded by tokens), and the int8 result is all-gathered: 5 bytes
+        per element cross NVLink instead of the 8 of an all-reduce.  Communication runs
+        on its own stream, so the exchange of one group overlaps the GEMMs of the next."""
+        tp = self.tp
+        n, rank = tp.size, tp.rank
+        bsz, tgt_len, e = residual.shape
+        bc = bsz // chunks
+        mc = bc * tgt_len
+        ms = mc // n
+        dev = residual.device
+        compute = torch.cuda.current_stream(dev)
+        comm = tp.comm_stream(dev)
+        layers = self.layers
+        first = layers[0].self_attn_layer_norm
+        res, h8, acc, ready, done = [], [], [], [], []
+        for c in range(chunks):
+            full = residual[c * bc:(c + 1) * bc]
+            h8.append(C.layernorm_q(full, first.weight, first.bias, first.eps))
+            res.append(full.reshape(mc, e)[rank * ms:(rank + 1) * ms].clone())
+            res[c].record_stream(comm)  # first consumed (and released) on the communication stream
+            acc.append(torch.empty((mc, e), dtype=torch.int32, device=dev))
+            ready.append(torch.cuda.Event())
+            done.append(torch.cuda.Event())
+            ready[c].record(compute)
+        comm.wait_stream(compute)
+
+        def exchange(c, scale, bias, ln):
+            """On the communication stream: reduce-scatter -> fused LayerNorm kernel -> all-gather."""
+            done[c].record(compute)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done[c])
+                shard = tp.reduce_scatter_int32(acc[c])
+                res[c], q = C.dq_add_layernorm_q_bias(shard, scale, bias, res[c], ln.weight, ln.bias, ln.eps)
+                tp.all_gather_into(h8[c].view(mc, e), q)
+                ready[c].record(comm)
+
+        nl = len(layers)
+        for i, layer in enumerate(layers):
+            attn = layer.self_attn
+            for c in range(chunks):
+                compute.wait_event(ready[c])
+                m = None if mask is None else mask[c * bc:(c + 1) * bc]
+                attn.forward_fused(h8[c], cache, i, past_len, m, out=acc[c], b0=c * bc)
+                exchange(c, attn.out_proj._scalar("a"), attn.out_proj.bias, layer.final_layer_norm)
+            next_ln = layers[i + 1].self_attn_layer_norm if i + 1 < nl else layer._identity_ln(dev)
+            for c in range(chunks):
+                compute.wait_event(ready[c])
+                f8 = layer.fc1._op(h8[c].view(mc, e))
+                C.gemm_i8_ex(f8, layer.fc2.weight, acc[c], epilogue=C.EPI_S32_RAW, m=mc, n=e, k=layer.local_ffn,
+                             lda=layer.local_ffn, ldb=layer.local_ffn, ldc=e)
+                exchange(c, layer.fc2._scalar("a"), layer.fc2.bias, next_ln)
+        out = torch.empty((bsz, tgt_len, e), dtype=torch.float32, device=dev)
+        with torch.cuda.stream(comm):
+            for c in range(chunks):
+                tp.all_gather_into(out[c * bc:(c + 1) * bc].view(mc, e), res[c])
+        compute.wait_stream(comm)
+        return out
+
     @torch.no_grad()
     def forward(self, input_ids: torch.LongTensor, attention_mask: Optional[torch.Tensor] = None,
                 past_key_values: Optional[StaticInt8KVCache] = None, use_cache: bool = False,
@@ -465,12 +530,16 @@ class Int8OPTDecoder(nn.Module):
                 residual = layer(residual, attention_mask=ref_mask)[0]
         else:
             residual = hidden.to(torch.float32).contiguous()
-            first = self.layers[0].self_attn_layer_norm
-            h8 = C.layernorm_q(residual, first.weight, first.bias, first.eps)
-            n = len(self.layers)
-            for i, layer in enumerate(self.layers):
-                next_ln = self.layers[i + 1].self_attn_layer_norm if i + 1 < n else None
-                residual, h8 = layer.forward_fused(residual, h8, cache, i, past_len, mask, next_ln)
+            chunks = self.tp.plan_chunks(bsz, tgt_len) if self.tp.size > 1 else 0
+            if chunks:
+                residual = self._layers_pipelined(residual, cache, past_len, mask, chunks)
+            else:
+                first = self.layers[0].self_attn_layer_norm
+                h8 = C.layernorm_q(residual, first.weight, first.bias, first.eps)
+                n = len(self.layers)
+                for i, layer in enumerate(self.layers):
+                    next_ln = self.layers[i + 1].self_attn_layer_norm if i + 1 < n else None
+                    residual, h8 = layer.forward_fused(residual, h8, cache, i, past_len, mask, next_ln)
             if cache is not None:
                 cache.length = src_len
             residual = residual.to(hidden.dtype)

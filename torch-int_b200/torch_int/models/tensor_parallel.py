@@ -17,10 +17,16 @@ import torch.distributed as dist
 
 
 class TensorParallel:
-    def __init__(self, size: int = 1, rank: int = 0, group=None):
+    def __init__(self, size: int = 1, rank: int = 0, group=None, max_chunks: int = 8,
+                 min_pipeline_tokens: int = 1024):
         self.size = size
         self.rank = rank
         self.group = group
+        self.max_chunks = max_chunks  # pipeline depth of the layer loop (groups of sequences)
+        # below this many tokens per group (decode steps, short prompts) the exchanges are latency
+        # bound and one all-reduce per exchange point is faster than the pipelined form
+        self.min_pipeline_tokens = min_pipeline_tokens
+        self._comm_streams = {}
 
     @staticmethod
     def single() -> "TensorParallel":
@@ -41,6 +47,37 @@ class TensorParallel:
             raise RuntimeError("tensor-parallel partial sums must be int32")
         dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
         return partial
+
+    def comm_stream(self, device):
+        """The stream the exchanges of the pipelined layer loop are enqueued on."""
+        key = torch.device(device).index
+        if key not in self._comm_streams:
+            self._comm_streams[key] = torch.cuda.Stream(device=device)
+        return self._comm_streams[key]
+
+    def plan_chunks(self, batch: int, tgt_len: int) -> int:
+        """Number of sequence groups for the pipelined layer loop: the largest divisor
+        of `batch` up to max_chunks whose groups have a token count divisible by the
+        rank count (rows are reduce-scattered evenly).  0 = use the all-reduce path."""
+        for c in range(min(self.max_chunks, batch), 0, -1):
+            tokens = (batch // c) * tgt_len
+            if batch % c == 0 and tokens % self.size == 0 and tokens >= self.min_pipeline_tokens:
+                return c
+        return 0
+
+    def reduce_scatter_int32(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum of the ranks' int32 partials [M, E]; rank r receives rows [r*M/n, (r+1)*M/n)."""
+        if partial.dtype != torch.int32 or partial.shape[0] % self.size != 0:
+            raise RuntimeError("reduce_scatter_int32 needs an int32 tensor whose rows divide evenly over the ranks")
+        out = torch.empty((partial.shape[0] // self.size,) + tuple(partial.shape[1:]), dtype=torch.int32,
+                          device=partial.device)
+        dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    def all_gather_into(self, full: torch.Tensor, shard: torch.Tensor) -> torch.Tensor:
+        """Concatenates the ranks' row shards into `full` (rank order)."""
+        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+        return full
 
     # ------------------------------------------------------------- weight sharding
     def _rows(self, t: torch.Tensor) -> torch.Tensor:
