@@ -233,6 +233,10 @@ class OptWorkload:
                 "hidden": self.cfg.hidden_size, "heads": self.cfg.num_attention_heads, "ffn": self.cfg.ffn_dim,
                 "vocab": self.cfg.vocab_size, "batch": self.batch, "prefill_len": self.seq,
                 "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single GPU",
+                "exchange": ("none" if n_gpus == 1 else
+                             "fused: GEMM-epilogue peer stores -> barrier -> reduce+LayerNorm kernel with peer stores"
+                             if (self.tp.use_peer_memory and self.tp._workspaces) else
+                             "NCCL reduce-scatter / all-gather on a communication stream"),
                 "weights": "random int8 uniform on [-127,127], analytic per-tensor scales x U(0.7,1.3)",
                 "logits": "all positions (fp16 lm_head)",
                 "l2": "per step the layers stream their int8 weights (>> 126 MB L2)"}

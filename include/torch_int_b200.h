@@ -113,6 +113,12 @@ typedef struct ti_gemm_desc {
   int32_t epilogue; /* enum ti_epilogue */
   int32_t tile_n;   /* 0 = automatic; else 32, 64, 128 or 256 */
   int32_t cta_pair; /* 0 = automatic; 1 = single-CTA tiles; 2 = 256x256 tiles on CTA pairs (tile_n 0 or 256) */
+  /* Optional row-block scatter of the output (batch == batch2 == 1): rows [i*scatter_rows,
+   * (i+1)*scatter_rows) are written to scatter_ptrs[i] with row stride ldc instead of C; the
+   * pointers may be peer-GPU memory (plain stores).  scatter_rows == 0: off.  This is the
+   * reduce-scatter step of a row-parallel linear fused into the GEMM epilogue. */
+  int64_t scatter_rows;
+  void* scatter_ptrs[8];
 } ti_gemm_desc;
 
 /* The reference has no strided entry point: its wrappers assume packed tensors
@@ -176,6 +182,29 @@ const char* ti_last_error(void);
  * 0 = ok, else the code of the first in-kernel wait that ran into its time
  * limit (the kernels never spin forever).  reset != 0 clears it. */
 int ti_device_status(int* status, int reset);
+
+/* ---- tensor-parallel exchange (no reference counterpart: the reference is single-GPU) ---- */
+
+/* For the `rows` rows this rank owns: sums `n_partials` int32 partial-sum slabs
+ * (stage[s * partial_stride + row * H + col], written by the ranks' GEMM epilogues through
+ * ti_gemm_desc.scatter_ptrs), then residual_out = residual + fma(scale, float(sum), bias) and
+ * q = LayerNorm-quantise(residual_out) as ti_dq_add_layernorm_q_bias does, and writes q to row
+ * (q_row_offset + row) of each of the n_dst buffers q_dst[i] (peer stores: the all-gather). */
+int ti_tp_reduce_layernorm_q(const int32_t* stage, int32_t n_partials, int64_t partial_stride,
+                             float scale, const float* bias, const float* residual, const float* gamma,
+                             const float* beta, float eps, float* residual_out, void* const* q_dst,
+                             int32_t n_dst, int64_t q_row_offset, int64_t rows, int64_t H, void* stream);
+
+/* Stream-ordered barrier over n <= 8 ranks.  pads[i] = rank i's pad (n 32-bit words, zeroed once,
+ * peer-accessible); epoch must increase by one per call on every rank.  Peer stores made by earlier
+ * work of `stream` are visible to the peers' work enqueued after their matching barrier.  The wait is
+ * bounded (2 s); on expiry the status word of ti_device_status is set to 105. */
+int ti_tp_barrier(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, void* stream);
+
+/* Caps the number of SMs the persistent GEMM/BMM grids of this process occupy (0 = all).  For callers
+ * that run collectives concurrently with the GEMMs and want the collective's CTAs to find free SMs.
+ * No reference counterpart (the reference has no multi-GPU path). */
+int ti_set_sm_limit(int sms);
 
 /* ABI version of this header (bumped on incompatible changes). */
 int ti_abi_version(void);

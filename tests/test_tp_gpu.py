@@ -45,7 +45,9 @@ def _rank_main(rank, world, port, ret):
             one = random_int8_opt(cfg, seed=21, device=dev, tp=TensorParallel.single(), consistent=True)
             ok = (torch.equal(logits, one(ids).logits) and torch.equal(logits4, one(ids4).logits)
                   and torch.equal(gen, one.generate_greedy(ids[:, :20], 5)))
-        ret[rank] = (ok, C.device_status())
+        tp = tp_model.model.decoder.tp
+        peer = tp.use_peer_memory and len(tp._workspaces) > 0  # the fused peer-memory exchange really ran
+        ret[rank] = (ok and peer, C.device_status())
     finally:
         dist.destroy_process_group()
 

@@ -149,6 +149,8 @@ int ti_gemm_i8_ex(const ti_gemm_desc* d, void* stream) {
   g.epilogue = d->epilogue;
   g.force_bn = d->tile_n;
   g.force_pair = d->cta_pair;
+  g.scatter_rows = d->scatter_rows;
+  for (int i = 0; i < 8; ++i) g.scatter_ptrs[i] = d->scatter_ptrs[i];
   return launch_gemm_i8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -196,6 +198,29 @@ int ti_device_status(int* status, int reset) {
     return TI_E_INVALID;
   }
   return device_status(status, reset != 0);
+}
+
+int ti_tp_reduce_layernorm_q(const int32_t* stage, int32_t n_partials, int64_t partial_stride,
+                             float scale, const float* bias, const float* residual, const float* gamma,
+                             const float* beta, float eps, float* residual_out, void* const* q_dst,
+                             int32_t n_dst, int64_t q_row_offset, int64_t rows, int64_t H, void* stream) {
+  return tp_reduce_layernorm_q(stage, n_partials, partial_stride, scale, bias, residual, gamma, beta, eps,
+                               residual_out, q_dst, n_dst, q_row_offset, rows, H,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int ti_tp_barrier(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, void* stream) {
+  int* status = status_word_ptr();
+  if (status == nullptr) {
+    set_error("ti_tp_barrier: cannot resolve the device status word");
+    return TI_E_CUDA;
+  }
+  return tp_barrier(pads, rank, n, epoch, status, static_cast<cudaStream_t>(stream));
+}
+
+int ti_set_sm_limit(int sms) {
+  set_sm_limit(sms);
+  return TI_OK;
 }
 
 int ti_abi_version(void) { return 1; }

@@ -39,12 +39,20 @@ struct GemmProblem {
   int epilogue = EPI_S32_RAW;
   int force_bn = 0;    // 0 = choose the N tile automatically
   int force_pair = 0;  // 0 = automatic, 1 = single-CTA tiles only, 2 = CTA-pair tiles (256 x 256)
+  // Optional row-block scatter of the output: rows [i*scatter_rows, (i+1)*scatter_rows) are
+  // written to scatter_ptrs[i] (row stride ldc) instead of C.  0 = off.
+  int64_t scatter_rows = 0;
+  void* scatter_ptrs[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 // Returns 0 or a negative TI_E_* code (message via set_error()).
 int launch_gemm_i8(const GemmProblem& p, cudaStream_t stream);
 
+// Caps the number of SMs the persistent GEMM grids use (0 = all SMs of the device).
+void set_sm_limit(int sms);
+
 // Status word set by kernels whose bounded waits gave up (0 = ok).
+int* status_word_ptr();
 int device_status(int* status, bool reset);
 
 // Error plumbing shared by all host entry points.

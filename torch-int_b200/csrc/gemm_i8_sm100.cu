@@ -52,6 +52,11 @@ struct KernelParams {
   float alpha, beta;
   int group_m;              // rasterisation: M tiles per column sweep
   int a_b1, a_b2, b_b1, b_b2;  // 0 where an operand is broadcast over a batch index (stride 0), else 1
+  // Row-block scatter of the output (tensor-parallel reduce-scatter fused into the epilogue):
+  // rows [i*scatter_rows, (i+1)*scatter_rows) go to scatter[i], which may be another GPU's memory
+  // reached by plain peer stores.  scatter_rows == 0: everything goes to C.
+  void* scatter[8];
+  int scatter_rows;
 };
 
 // PAIR = false: one CTA computes a 128 x BN tile (tcgen05 cta_group::1).
@@ -67,7 +72,8 @@ struct Cfg {
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
   static constexpr int B_BYTES = B_ROWS * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int AUX_BYTES = 2 * BN * 4 + 256;  // bias tiles + barriers
+  static constexpr int XPOSE_BYTES = 4 * 32 * 144;       // per epilogue warp: 32 rows x (128 + 16) bytes
+  static constexpr int AUX_BYTES = 2 * BN * 4 + 256 + XPOSE_BYTES;  // bias tiles + barriers + store staging
   static constexpr int STAGES_RAW = (SMEM_BUDGET - 1024 - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES;
@@ -163,6 +169,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* aux = smem + C::STAGES * C::STAGE_BYTES;
   uint32_t* bias_smem = reinterpret_cast<uint32_t*>(aux);  // [2][BN]
   uint64_t* bars = reinterpret_cast<uint64_t*>(aux + 2 * BN * 4);
+  uint8_t* xpose = aux + 2 * BN * 4 + 256;  // [4 warps][32 rows][144 bytes]
   uint64_t* full_bar = bars;                    // [STAGES]  (PAIR: only the leader's are used)
   uint64_t* empty_bar = bars + C::STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * C::STAGES;   // [2]
@@ -324,33 +331,44 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!ok) break;
       tc_fence_after();
 
-      const int row = tc.m_tile * C::TILE_M + static_cast<int>(rank) * BM + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
-      uint8_t* crow = static_cast<uint8_t*>(p.C) +
-                      (static_cast<long long>(tc.b2) * p.stride2C +
-                       static_cast<long long>(tc.b1) * p.strideC +
-                       static_cast<long long>(row) * p.ldc + n0) *
-                          T::kOutBytes;
+      const int row0 = tc.m_tile * C::TILE_M + static_cast<int>(rank) * BM + quarter * 32;  // first row of this warp
+      // Address of output row r (this tile's column 0).
+      auto row_ptr = [&](int r) -> uint8_t* {
+        if (p.scatter_rows > 0) {
+          const int owner = min(r / p.scatter_rows, 7);
+          return static_cast<uint8_t*>(p.scatter[owner]) +
+                 (static_cast<long long>(r - owner * p.scatter_rows) * p.ldc + n0) * T::kOutBytes;
+        }
+        return static_cast<uint8_t*>(p.C) +
+               (static_cast<long long>(tc.b2) * p.stride2C + static_cast<long long>(tc.b1) * p.strideC +
+                static_cast<long long>(r) * p.ldc + n0) *
+                   T::kOutBytes;
+      };
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       const uint32_t* bs = bias_smem + buf * BN;
+      if constexpr (T::kOutS8) {
+        // int8 rows: a thread owns one row and writes its 32 bytes of each chunk as two 16-byte stores
+        // (one full 32-byte sector).
+        const int row = row0 + lane;
+        const bool row_ok = row < p.M;
+        uint8_t* crow = row_ptr(row_ok ? row : 0);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        if (n0 + c * 32 >= p.N) break;  // uniform over the CTA
-        uint32_t v[32];
-        __syncwarp();
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
+        for (int c = 0; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;  // uniform over the CTA
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (row_ok) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            uint4 tb = make_uint4(0, 0, 0, 0);
-            if constexpr (T::kHasBias) tb = reinterpret_cast<const uint4*>(bs)[c * 8 + q];
-            v[q * 4 + 0] = epilogue_one<EPI>(v[q * 4 + 0], tb.x, p.alpha);
-            v[q * 4 + 1] = epilogue_one<EPI>(v[q * 4 + 1], tb.y, p.alpha);
-            v[q * 4 + 2] = epilogue_one<EPI>(v[q * 4 + 2], tb.z, p.alpha);
-            v[q * 4 + 3] = epilogue_one<EPI>(v[q * 4 + 3], tb.w, p.alpha);
-          }
-          if constexpr (T::kOutS8) {
+            for (int q = 0; q < 8; ++q) {
+              uint4 tb = make_uint4(0, 0, 0, 0);
+              if constexpr (T::kHasBias) tb = reinterpret_cast<const uint4*>(bs)[c * 8 + q];
+              v[q * 4 + 0] = epilogue_one<EPI>(v[q * 4 + 0], tb.x, p.alpha);
+              v[q * 4 + 1] = epilogue_one<EPI>(v[q * 4 + 1], tb.y, p.alpha);
+              v[q * 4 + 2] = epilogue_one<EPI>(v[q * 4 + 2], tb.z, p.alpha);
+              v[q * 4 + 3] = epilogue_one<EPI>(v[q * 4 + 3], tb.w, p.alpha);
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               if (n0 + c * 32 + h * 16 < p.N) {
@@ -362,14 +380,44 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 *reinterpret_cast<uint4*>(crow + c * 32 + h * 16) = o;
               }
             }
-          } else {
+          }
+        }
+      } else {
+        // 32-bit outputs: the 32 rows x 128 bytes of a chunk are transposed through a per-warp
+        // shared-memory patch so that eight lanes write one row's 128 contiguous bytes - full lines
+        // for local HBM and efficient packets when the destination is a peer GPU.
+        uint8_t* patch = xpose + quarter * (32 * 144);
+        const int sub = lane >> 3, piece = lane & 7;  // this lane stores piece `piece` of rows sub, sub+4, ...
+        uint8_t* rp[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              if (n0 + c * 32 + q * 4 < p.N) {
-                uint4 o = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                *reinterpret_cast<uint4*>(crow + (c * 32 + q * 4) * 4) = o;
-              }
-            }
+        for (int i = 0; i < 8; ++i) {
+          const int r = row0 + i * 4 + sub;
+          rp[i] = r < p.M ? row_ptr(r) + piece * 16 : nullptr;
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;  // uniform over the CTA
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 tb = make_uint4(0, 0, 0, 0);
+            if constexpr (T::kHasBias) tb = reinterpret_cast<const uint4*>(bs)[c * 8 + q];
+            uint4 o;
+            o.x = epilogue_one<EPI>(v[q * 4 + 0], tb.x, p.alpha);
+            o.y = epilogue_one<EPI>(v[q * 4 + 1], tb.y, p.alpha);
+            o.z = epilogue_one<EPI>(v[q * 4 + 2], tb.z, p.alpha);
+            o.w = epilogue_one<EPI>(v[q * 4 + 3], tb.w, p.alpha);
+            *reinterpret_cast<uint4*>(patch + lane * 144 + q * 16) = o;
+          }
+          __syncwarp();
+          const bool col_ok = n0 + c * 32 + piece * 4 < p.N;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 o = *reinterpret_cast<const uint4*>(patch + (i * 4 + sub) * 144 + piece * 16);
+            if (col_ok && rp[i] != nullptr) *reinterpret_cast<uint4*>(rp[i] + c * 128) = o;
           }
         }
       }
@@ -467,6 +515,10 @@ bool make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t K, int64_t ro
   return true;
 }
 
+// Upper bound on the SMs the persistent GEMM grid occupies (0 = all).  A caller that
+// overlaps collectives with the GEMMs lowers it so that the collective's CTAs find free SMs.
+int g_sm_limit = 0;
+
 int num_sms() {
   static int cached[64] = {0};
   int dev = 0;
@@ -477,7 +529,8 @@ int num_sms() {
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     cached[dev] = n > 0 ? n : 148;
   }
-  return cached[dev];
+  const int n = cached[dev];
+  return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
 }
 
 template <int BN, int EPI, bool PAIR>
@@ -522,6 +575,8 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
   p.a_b2 = (g.stride2A != 0 && g.batch2 > 1) ? 1 : 0;
   p.b_b1 = (g.strideB != 0 && g.batch > 1) ? 1 : 0;
   p.b_b2 = (g.stride2B != 0 && g.batch2 > 1) ? 1 : 0;
+  p.scatter_rows = static_cast<int>(g.scatter_rows);
+  for (int i = 0; i < 8; ++i) p.scatter[i] = g.scatter_rows > 0 ? g.scatter_ptrs[i] : nullptr;
   const int sms = num_sms();
   const long long workers = PAIR ? sms / 2 : sms;  // CTAs, or CTA pairs
   const int grid = static_cast<int>(p.total_tiles < workers ? p.total_tiles : workers) * (PAIR ? 2 : 1);
@@ -611,9 +666,21 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
     set_error("K must be positive");
     return TI_E_INVALID;
   }
-  if (!g.A || !g.B || !g.C) {
+  if (!g.A || !g.B || (!g.C && g.scatter_rows == 0)) {
     set_error("null operand pointer");
     return TI_E_INVALID;
+  }
+  if (g.scatter_rows != 0) {
+    const int64_t blocks = g.scatter_rows > 0 ? (g.M + g.scatter_rows - 1) / g.scatter_rows : 0;
+    if (g.scatter_rows < 0 || blocks > 8 || g.batch != 1 || g.batch2 != 1) {
+      set_error("output scatter needs batch == 1 and at most 8 row blocks");
+      return TI_E_INVALID;
+    }
+    for (int64_t i = 0; i < blocks; ++i)
+      if (!g.scatter_ptrs[i] || (reinterpret_cast<uintptr_t>(g.scatter_ptrs[i]) & 15)) {
+        set_error("output scatter pointers must be non-null and 16-byte aligned");
+        return TI_E_INVALID;
+      }
   }
   const bool out_s8 = g.epilogue == EPI_S8_BIAS_S8 || g.epilogue == EPI_S8_BIAS_S8_RELU ||
                       g.epilogue == EPI_S8_ALPHA;
@@ -647,7 +714,7 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
     return TI_E_INVALID;
   }
   if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) |
-       reinterpret_cast<uintptr_t>(g.C)) & 15) {
+       (g.scatter_rows ? 0 : reinterpret_cast<uintptr_t>(g.C))) & 15) {
     set_error("operand and output pointers must be 16-byte aligned");
     return TI_E_INVALID;
   }
@@ -677,6 +744,15 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
   set_error("unknown epilogue %d", g.epilogue);
   return TI_E_INVALID;
 }
+
+// Device address of the status word, for kernels of other translation units.
+int* status_word_ptr() {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, ti_kernel_status) != cudaSuccess) return nullptr;
+  return static_cast<int*>(p);
+}
+
+void set_sm_limit(int sms) { g_sm_limit = sms > 0 ? sms : 0; }
 
 // Reads (and optionally clears) the status word the kernels of this file set
 // when a bounded wait gives up.  Synchronises the device.

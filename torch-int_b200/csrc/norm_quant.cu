@@ -429,6 +429,120 @@ transpose_values_kernel(const int8_t* __restrict__ v, int8_t* __restrict__ vt, i
   }
 }
 
+// ---------------------------------------------------------------- tensor parallel
+struct PeerPtrs {
+  void* p[8];
+};
+
+// Second half of a row-parallel linear under tensor parallelism, for the rows this
+// rank owns: `stage` holds one int32 partial-sum slab per rank ([n_partials][rows][H],
+// written by the ranks' GEMM epilogues through peer stores).  Per row:
+//   acc = sum of the partials (exact integer addition: any order gives the same bits)
+//   r   = residual + fma(scale, float(acc), bias)        (the fp32-output linear + residual add)
+//   q   = int8(rne(clamp(LayerNorm(r) * gamma + beta)))
+// r stays on this rank (the residual stream is sharded by rows); q is written to the
+// same row of every rank's activation buffer (q_dst, peer stores): the all-gather.
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+tp_reduce_layernorm_q_kernel(const int32_t* __restrict__ stage, int n_partials, long long partial_stride,
+                             float scale, const float* __restrict__ in_bias,
+                             const float* __restrict__ res, const float* __restrict__ gamma,
+                             const float* __restrict__ beta, float eps, float* __restrict__ res_out,
+                             PeerPtrs q_dst, int n_dst, long long q_row_offset, int H) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const int h4 = H >> 2;
+  float4 v[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) {
+      const int32_t* ir = stage + row * H + 4 * i;
+      int4 a = *reinterpret_cast<const int4*>(ir);
+      for (int s = 1; s < n_partials; ++s) {
+        const int4 b = *reinterpret_cast<const int4*>(ir + s * partial_stride);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      const float4 r = *reinterpret_cast<const float4*>(res + row * H + 4 * i);
+      const float4 bb = *reinterpret_cast<const float4*>(in_bias + 4 * i);
+      float4 o;
+      o.x = r.x + __fmaf_rn(scale, __int2float_rn(a.x), bb.x);
+      o.y = r.y + __fmaf_rn(scale, __int2float_rn(a.y), bb.y);
+      o.z = r.z + __fmaf_rn(scale, __int2float_rn(a.z), bb.z);
+      o.w = r.w + __fmaf_rn(scale, __int2float_rn(a.w), bb.w);
+      *reinterpret_cast<float4*>(res_out + row * H + 4 * i) = o;
+      v[j] = o;
+    }
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+  }
+  const float mean = block_reduce<THREADS, false>(s, scratch) / static_cast<float>(H);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) {
+      const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+      ss += (a * a + b * b) + (c * c + d * d);
+    }
+  }
+  const float var = block_reduce<THREADS, false>(ss, scratch) / static_cast<float>(H);
+  const float rstd = __fdiv_rn(1.f, __fsqrt_rn(var + eps));
+  const long long qoff = (q_row_offset + row) * H;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < h4) {
+      const float4 g = *reinterpret_cast<const float4*>(gamma + 4 * i);
+      const float4 b = *reinterpret_cast<const float4*>(beta + 4 * i);
+      const uint32_t packed = pack_s8x4(__fmaf_rn((v[j].x - mean) * rstd, g.x, b.x),
+                                        __fmaf_rn((v[j].y - mean) * rstd, g.y, b.y),
+                                        __fmaf_rn((v[j].z - mean) * rstd, g.z, b.z),
+                                        __fmaf_rn((v[j].w - mean) * rstd, g.w, b.w));
+      for (int d = 0; d < n_dst; ++d)
+        *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(q_dst.p[d]) + qoff + 4 * i) = packed;
+    }
+  }
+}
+
+// Barrier over the ranks of a tensor-parallel group, enqueued on a stream.  Every rank
+// owns a pad of one 32-bit word per rank in peer-accessible memory.  Thread t signals
+// rank t (stores `epoch` into word [rank] of t's pad, system-scope release, after a
+// system fence that orders the peer stores of earlier kernels of this stream before it)
+// and then waits until rank t's signal for this epoch has arrived in its own pad.  The
+// wait is bounded: after `limit_ns` it records an error in *status and returns.
+__global__ void tp_barrier_kernel(PeerPtrs pads, int rank, int n, uint32_t epoch, int* status,
+                                  unsigned long long limit_ns) {
+  const int t = threadIdx.x;
+  if (t < n) {
+    __threadfence_system();
+    uint32_t* theirs = static_cast<uint32_t*>(pads.p[t]) + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+    const uint32_t* mine = static_cast<const uint32_t*>(pads.p[rank]) + t;
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int>(v - epoch) >= 0) break;
+      if ((it & 63) == 63) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > limit_ns) {
+          atomicCAS(status, 0, 105);
+          break;
+        }
+      }
+    }
+    __threadfence_system();
+  }
+}
+
 template <typename F>
 int check_launch(const char* name, F&& f) {
   f();
@@ -613,6 +727,66 @@ int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch
                       static_cast<int>(heads), lds, ldo, causal);
                 }));
   return rc;
+}
+
+int tp_reduce_layernorm_q(const int32_t* stage, int n_partials, int64_t partial_stride, float scale,
+                          const float* in_bias, const float* res, const float* gamma, const float* beta,
+                          float eps, float* res_out, void* const* q_dst, int n_dst, int64_t q_row_offset,
+                          int64_t rows, int64_t H, cudaStream_t stream) {
+  if (rows < 0 || H <= 0 || n_partials < 1 || n_partials > 8 || n_dst < 1 || n_dst > 8) {
+    set_error("tp_reduce_layernorm_q: bad shape");
+    return TI_E_INVALID;
+  }
+  if (rows == 0) return TI_OK;
+  const int h4 = static_cast<int>(H / 4);
+  if (H % 4 != 0 || h4 > 256 * kMaxVpt || rows > 0x7FFFFFFF || partial_stride % 4 != 0 || !stage || !in_bias ||
+      !res || !gamma || !beta || !res_out || !q_dst || !aligned16(stage) || !aligned16(in_bias) || !aligned16(res) ||
+      !aligned16(gamma) || !aligned16(beta) || !aligned16(res_out)) {
+    set_error("tp_reduce_layernorm_q: H must be a multiple of 4 and at most %d, pointers 16-byte aligned",
+              256 * kMaxVpt * 4);
+    return TI_E_INVALID;
+  }
+  PeerPtrs dst;
+  for (int i = 0; i < 8; ++i) {
+    dst.p[i] = i < n_dst ? q_dst[i] : nullptr;
+    if (i < n_dst && (!q_dst[i] || (reinterpret_cast<uintptr_t>(q_dst[i]) & 3))) {
+      set_error("tp_reduce_layernorm_q: bad destination pointer %d", i);
+      return TI_E_INVALID;
+    }
+  }
+  const unsigned grid = static_cast<unsigned>(rows);
+  if (h4 <= 128)
+    return check_launch("tp_reduce_layernorm_q", [&] {
+      tp_reduce_layernorm_q_kernel<128, 1><<<grid, 128, 0, stream>>>(
+          stage, n_partials, partial_stride, scale, in_bias, res, gamma, beta, eps, res_out, dst, n_dst,
+          q_row_offset, static_cast<int>(H));
+    });
+  const int vpt = (h4 + 255) / 256;
+  int rc = TI_OK;
+  TI_VPT_SWITCH(vpt, rc = check_launch("tp_reduce_layernorm_q", [&] {
+                  tp_reduce_layernorm_q_kernel<256, VPT><<<grid, 256, 0, stream>>>(
+                      stage, n_partials, partial_stride, scale, in_bias, res, gamma, beta, eps, res_out, dst,
+                      n_dst, q_row_offset, static_cast<int>(H));
+                }));
+  return rc;
+}
+
+int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_word, cudaStream_t stream) {
+  if (n < 1 || n > 8 || rank < 0 || rank >= n || !pads || !status_word) {
+    set_error("tp_barrier: bad arguments");
+    return TI_E_INVALID;
+  }
+  PeerPtrs p;
+  for (int i = 0; i < 8; ++i) {
+    p.p[i] = i < n ? pads[i] : nullptr;
+    if (i < n && !pads[i]) {
+      set_error("tp_barrier: null pad pointer");
+      return TI_E_INVALID;
+    }
+  }
+  return check_launch("tp_barrier", [&] {
+    tp_barrier_kernel<<<1, 32, 0, stream>>>(p, rank, n, epoch, status_word, 2000000000ull);
+  });
 }
 
 int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,

@@ -21,6 +21,13 @@ int dq_add_layernorm_q(const int32_t* in, float scale, const void* res, int res_
 int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch_heads, int64_t heads,
               int64_t T, int64_t S, int64_t lds, int64_t ldo, int causal, cudaStream_t stream);
 
+// Tensor-parallel exchange kernels (see the kernels in norm_quant.cu).
+int tp_reduce_layernorm_q(const int32_t* stage, int n_partials, int64_t partial_stride, float scale,
+                          const float* in_bias, const float* res, const float* gamma, const float* beta,
+                          float eps, float* res_out, void* const* q_dst, int n_dst, int64_t q_row_offset,
+                          int64_t rows, int64_t H, cudaStream_t stream);
+int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_word, cudaStream_t stream);
+
 // int8 v [B, T, H, D] -> vt [B, H, D, ld_out], written at columns [col0, col0 + T).
 int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
                      int64_t ld_out, int64_t col0, cudaStream_t stream);

@@ -63,6 +63,7 @@ class _GemmDesc(ctypes.Structure):
         ("stride2A", _i64), ("stride2B", _i64), ("stride2C", _i64),
         ("alpha", _f32), ("beta", _f32),
         ("epilogue", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
+        ("scatter_rows", _i64), ("scatter_ptrs", _ptr * 8),
     ]
 
 
@@ -90,10 +91,15 @@ _c_dq_add_ln_q_bias = _sig("ti_dq_add_layernorm_q_bias",
                            [_ptr, _f32, _ptr, _ptr, _i32, _ptr, _ptr, _f32, _ptr, _ptr, _i64, _i64, _ptr])
 _c_ln_q = _sig("ti_layernorm_q", [_ptr, _i32, _ptr, _ptr, _f32, _ptr, _i64, _i64, _ptr])
 _c_softmax_q = _sig("ti_softmax_q", [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _ptr])
+_c_tp_reduce_ln_q = _sig("ti_tp_reduce_layernorm_q",
+                          [_ptr, _i32, _i64, _f32, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, ctypes.POINTER(_ptr), _i32,
+                           _i64, _i64, _i64, _ptr])
+_c_tp_barrier = _sig("ti_tp_barrier", [ctypes.POINTER(_ptr), _i32, _i32, ctypes.c_uint32, _ptr])
 _c_transpose_values = _sig("ti_transpose_values", [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr])
 _c_last_error = _sig("ti_last_error", [], ctypes.c_char_p)
 _c_device_status = _sig("ti_device_status", [ctypes.POINTER(ctypes.c_int), _i32])
 _c_abi_version = _sig("ti_abi_version", [])
+_c_set_sm_limit = _sig("ti_set_sm_limit", [_i32])
 
 if _c_abi_version() != 1:
     raise ImportError("torch_int._CUDA: libtorch_int_b200.so has an unexpected ABI version")
@@ -359,13 +365,18 @@ def softmax_q(scores, mask=None, num_heads=1, causal=-1):
 
 def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, lda, ldb, ldc,
                stride_a=0, stride_b=0, stride_c=0, stride2_a=0, stride2_b=0, stride2_c=0,
-               alpha=1.0, beta=0.0, tile_n=0, cta_pair=0):
+               alpha=1.0, beta=0.0, tile_n=0, cta_pair=0, scatter_ptrs=None, scatter_rows=0):
     """Strided form (ti_gemm_i8_ex): operands are addressed through explicit
     element strides starting at each tensor's data pointer, so views can be
-    multiplied without contiguous copies.  Writes into `out` and returns it."""
+    multiplied without contiguous copies.  Writes into `out` and returns it.
+    With scatter_ptrs (device addresses, possibly of peer GPUs) and scatter_rows, row
+    block i of the output goes to scatter_ptrs[i] instead and `out` may be None."""
     for t, name in ((a, "a"), (b, "b")):
         if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.int8):
             raise RuntimeError(f"{name} must be a CUDA int8 tensor")
+    if scatter_rows:
+        return _gemm_scatter(a, b, bias, epilogue, m, n, k, lda, ldb, ldc, alpha, beta, tile_n, cta_pair,
+                             scatter_ptrs, scatter_rows)
     if not (isinstance(out, torch.Tensor) and out.is_cuda and out.dtype == _EPI_OUT_DTYPE[epilogue]):
         raise RuntimeError(f"out must be a CUDA tensor of dtype {_EPI_OUT_DTYPE[epilogue]}")
     if a.device != b.device or a.device != out.device:
@@ -399,6 +410,52 @@ def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, ld
     return out
 
 
+def _gemm_scatter(a, b, bias, epilogue, m, n, k, lda, ldb, ldc, alpha, beta, tile_n, cta_pair, ptrs, rows):
+    if len(ptrs) * rows < m or len(ptrs) > 8:
+        raise RuntimeError("scatter_ptrs must cover all rows with at most 8 blocks")
+    d = _GemmDesc()
+    d.A, d.B, d.C = a.data_ptr(), b.data_ptr(), None
+    d.bias = _bias_vector(bias, n, _EPI_BIAS_DTYPE[epilogue], a.device).data_ptr() if epilogue in _EPI_BIAS_DTYPE else None
+    d.M, d.N, d.K, d.batch, d.batch2 = m, n, k, 1, 1
+    d.lda, d.ldb, d.ldc = lda, ldb, ldc
+    d.alpha, d.beta, d.epilogue, d.tile_n, d.cta_pair = float(alpha), float(beta), epilogue, tile_n, cta_pair
+    d.scatter_rows = rows
+    for i, ptr in enumerate(ptrs):
+        d.scatter_ptrs[i] = ptr
+    with _on_device(a.device):
+        rc = _c_gemm_ex(ctypes.byref(d), _stream_ptr(a.device))
+    _check(rc)
+    return None
+
+
+def tp_reduce_layernorm_q(stage, n_partials, partial_stride, scale, bias, residual, gamma, beta, epsilon,
+                          q_dst_ptrs, q_row_offset):
+    """Tensor-parallel exchange, second half (ti_tp_reduce_layernorm_q): stage int32
+    [n_partials, rows, H] (this rank's rows), residual fp32 [rows, H]; returns the new
+    residual; the int8 LayerNorm output is written to the buffers at q_dst_ptrs."""
+    _require(stage, "stage", torch.int32)
+    _require(residual, "residual", torch.float32, 2)
+    rows, h = residual.shape
+    g, b = _affine(gamma, beta, h, residual.device)
+    ib = _bias_vector(bias, h, torch.float32, residual.device)
+    out = torch.empty_like(residual)
+    arr = (_ptr * len(q_dst_ptrs))(*q_dst_ptrs)
+    with _on_device(residual.device):
+        rc = _c_tp_reduce_ln_q(stage.data_ptr(), n_partials, partial_stride, float(scale), ib.data_ptr(),
+                               residual.data_ptr(), g.data_ptr(), b.data_ptr(), float(epsilon), out.data_ptr(),
+                               arr, len(q_dst_ptrs), q_row_offset, rows, h, _stream_ptr(residual.device))
+    _check(rc)
+    return out
+
+
+def tp_barrier(pad_ptrs, rank, epoch, device):
+    """Stream-ordered barrier over the ranks owning the pads at pad_ptrs (ti_tp_barrier)."""
+    arr = (_ptr * len(pad_ptrs))(*pad_ptrs)
+    with _on_device(device):
+        rc = _c_tp_barrier(arr, rank, len(pad_ptrs), epoch & 0xFFFFFFFF, _stream_ptr(device))
+    _check(rc)
+
+
 def transpose_values(v, vt, col0=0):
     """int8 v [B, T, H, D] -> vt [B, H, D, cap] at columns [col0, col0 + T): the transposed
     value layout P.V consumes.  Replaces transpose(1, 2).contiguous() of torch_int/models/opt.py:180."""
@@ -411,6 +468,11 @@ def transpose_values(v, vt, col0=0):
         rc = _c_transpose_values(v.data_ptr(), vt.data_ptr(), b, t, h, d, vt.shape[3], col0, _stream_ptr(v.device))
     _check(rc)
     return vt
+
+
+def set_sm_limit(sms):
+    """Caps the SMs the persistent GEMM grids occupy (0 = all); see ti_set_sm_limit."""
+    _c_set_sm_limit(int(sms))
 
 
 def device_status(reset=True):

@@ -144,7 +144,8 @@ class Int8OPTAttention(nn.Module):
 
     @torch.no_grad()
     def forward_fused(self, hidden_int8, cache: Optional[StaticInt8KVCache], layer_idx: int, past_len: int,
-                      mask: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, b0: int = 0):
+                      mask: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, b0: int = 0,
+                      context_only: bool = False):
         """int8 [B,T,E] -> int32 partial sums of out_proj [B*T, E] (this rank's input
         slice; bias and scale are applied after the reduction over the ranks).  `out`:
         optional destination; `b0`: index of the first of these sequences in the cache."""
@@ -172,6 +173,8 @@ class Int8OPTAttention(nn.Module):
         causal = past_len if mask is None else -1
         ctx = self.attention_core(q.view(bsz, tgt_len, el), k_rows, vt, bsz, tgt_len, src_len, src_pad,
                                   k_row_stride, k_batch_stride, vt_row_stride, causal, mask)
+        if context_only:
+            return ctx  # int8 [B,T,Hl*D]: the caller runs out_proj itself
         ctx2d = ctx.view(-1, el)
         acc = out if out is not None else torch.empty((ctx2d.shape[0], self.embed_dim), dtype=torch.int32,
                                                       device=ctx.device)
@@ -447,27 +450,53 @@ class Int8OPTDecoder(nn.Module):
         comm = tp.comm_stream(dev)
         layers = self.layers
         first = layers[0].self_attn_layer_norm
+        ws = tp.peer_workspace(chunks, mc, e, dev)
         res, h8, acc, ready, done = [], [], [], [], []
         for c in range(chunks):
             full = residual[c * bc:(c + 1) * bc]
-            h8.append(C.layernorm_q(full, first.weight, first.bias, first.eps))
+            q0 = C.layernorm_q(full, first.weight, first.bias, first.eps)
+            if ws is not None:
+                ws.h8[c].copy_(q0.view(mc, e))
+                h8.append(ws.h8[c].view(bc, tgt_len, e))
+                acc.append(None)
+            else:
+                h8.append(q0)
+                acc.append(torch.empty((mc, e), dtype=torch.int32, device=dev))
             res.append(full.reshape(mc, e)[rank * ms:(rank + 1) * ms].clone())
             res[c].record_stream(comm)  # first consumed (and released) on the communication stream
-            acc.append(torch.empty((mc, e), dtype=torch.int32, device=dev))
             ready.append(torch.cuda.Event())
             done.append(torch.cuda.Event())
             ready[c].record(compute)
         comm.wait_stream(compute)
 
         def exchange(c, scale, bias, ln):
-            """On the communication stream: reduce-scatter -> fused LayerNorm kernel -> all-gather."""
+            """On the communication stream.  Peer-memory form: the GEMM epilogue has already
+            stored this rank's partial sums into the owners' stage slabs; barrier, then one kernel
+            sums the slabs of my rows, applies scale/bias/residual/LayerNorm/quantise and stores the
+            int8 rows into every rank's activation buffer; barrier.  NCCL form: reduce-scatter ->
+            fused LayerNorm kernel -> all-gather."""
             done[c].record(compute)
             with torch.cuda.stream(comm):
                 comm.wait_event(done[c])
-                shard = tp.reduce_scatter_int32(acc[c])
-                res[c], q = C.dq_add_layernorm_q_bias(shard, scale, bias, res[c], ln.weight, ln.bias, ln.eps)
-                tp.all_gather_into(h8[c].view(mc, e), q)
+                if ws is not None:
+                    ws.barrier()
+                    res[c] = C.tp_reduce_layernorm_q(ws.stage[c], n, ms * e, scale, bias, res[c], ln.weight,
+                                                     ln.bias, ln.eps, ws.q_dst_ptrs(c), rank * ms)
+                    ws.barrier()
+                else:
+                    shard = tp.reduce_scatter_int32(acc[c])
+                    res[c], q = C.dq_add_layernorm_q_bias(shard, scale, bias, res[c], ln.weight, ln.bias, ln.eps)
+                    tp.all_gather_into(h8[c].view(mc, e), q)
                 ready[c].record(comm)
+
+        def row_parallel(c, x2d, weight, k):
+            """int32 partial sums of a row-parallel linear for chunk c: to the owners' stage slabs
+            (peer stores from the GEMM epilogue) or to the local buffer for NCCL."""
+            if ws is not None:
+                C.gemm_i8_ex(x2d, weight, None, epilogue=C.EPI_S32_RAW, m=mc, n=e, k=k, lda=k, ldb=k, ldc=e,
+                             scatter_ptrs=ws.scatter_ptrs(c), scatter_rows=ms)
+            else:
+                C.gemm_i8_ex(x2d, weight, acc[c], epilogue=C.EPI_S32_RAW, m=mc, n=e, k=k, lda=k, ldb=k, ldc=e)
 
         nl = len(layers)
         for i, layer in enumerate(layers):
@@ -475,14 +504,14 @@ class Int8OPTDecoder(nn.Module):
             for c in range(chunks):
                 compute.wait_event(ready[c])
                 m = None if mask is None else mask[c * bc:(c + 1) * bc]
-                attn.forward_fused(h8[c], cache, i, past_len, m, out=acc[c], b0=c * bc)
+                ctx = attn.forward_fused(h8[c], cache, i, past_len, m, b0=c * bc, context_only=True)
+                row_parallel(c, ctx.view(mc, attn.local_dim), attn.out_proj.weight, attn.local_dim)
                 exchange(c, attn.out_proj._scalar("a"), attn.out_proj.bias, layer.final_layer_norm)
             next_ln = layers[i + 1].self_attn_layer_norm if i + 1 < nl else layer._identity_ln(dev)
             for c in range(chunks):
                 compute.wait_event(ready[c])
                 f8 = layer.fc1._op(h8[c].view(mc, e))
-                C.gemm_i8_ex(f8, layer.fc2.weight, acc[c], epilogue=C.EPI_S32_RAW, m=mc, n=e, k=layer.local_ffn,
-                             lda=layer.local_ffn, ldb=layer.local_ffn, ldc=e)
+                row_parallel(c, f8, layer.fc2.weight, layer.local_ffn)
                 exchange(c, layer.fc2._scalar("a"), layer.fc2.bias, next_ln)
         out = torch.empty((bsz, tgt_len, e), dtype=torch.float32, device=dev)
         with torch.cuda.stream(comm):

@@ -10,6 +10,7 @@ epilogue (scale, bias, residual add, LayerNorm, quantise) then runs once on the
 reduced value on every rank.  The reference has no multi-GPU path
 (no torch.distributed call in torch_int/); this file is new functionality.
 """
+import os
 from typing import Dict, Optional
 
 import torch
@@ -27,6 +28,11 @@ class TensorParallel:
         # bound and one all-reduce per exchange point is faster than the pipelined form
         self.min_pipeline_tokens = min_pipeline_tokens
         self._comm_streams = {}
+        self._workspaces = {}
+        # fuse the exchanges into the GEMM epilogue / LayerNorm kernel through peer stores
+        self.use_peer_memory = os.environ.get("TI_TP_PEER_MEMORY", "1") != "0"
+        # SMs the GEMM grids may use while exchanges overlap them (0 = all); TI_TP_GEMM_SMS overrides
+        self.gemm_sm_limit = int(os.environ.get("TI_TP_GEMM_SMS", "0"))
 
     @staticmethod
     def single() -> "TensorParallel":
@@ -79,6 +85,24 @@ class TensorParallel:
         dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
         return full
 
+    def peer_workspace(self, chunks: int, mc: int, e: int, device):
+        """Peer-accessible buffers for the fused exchange of the pipelined layer loop, or
+        None when symmetric memory is unavailable (then NCCL collectives are used)."""
+        if not self.use_peer_memory:
+            return None
+        key = (chunks, mc, e, torch.device(device).index)
+        ws = self._workspaces.get(key)
+        if ws is None:
+            try:
+                ws = PeerWorkspace(self, chunks, mc, e, device)
+            except Exception as exc:  # noqa: BLE001 - any failure means "fall back to NCCL"
+                import warnings
+                warnings.warn(f"tensor parallel: peer memory unavailable ({exc}); using NCCL collectives")
+                self.use_peer_memory = False
+                return None
+            self._workspaces[key] = ws
+        return ws
+
     # ------------------------------------------------------------- weight sharding
     def _rows(self, t: torch.Tensor) -> torch.Tensor:
         n = t.shape[0]
@@ -113,3 +137,55 @@ class TensorParallel:
             else:
                 out[name] = t
         return out
+
+
+class PeerWorkspace:
+    """Symmetric (same layout on every rank, mapped into every rank) buffers of the fused
+    tensor-parallel exchange:
+      stage [chunks][n][ms][e] int32  slab s of chunk c receives rank s's partial sums of my rows
+      h8    [chunks][mc][e]   int8   the LayerNorm-quantise output of all rows (every owner writes its rows)
+      pads  [n] uint32               barrier words
+    Allocated with torch's symmetric memory (cuMem mappings exchanged between the processes);
+    all traffic is plain peer loads/stores issued by this library's kernels."""
+
+    def __init__(self, tp: "TensorParallel", chunks: int, mc: int, e: int, device):
+        import torch.distributed._symmetric_memory as symm
+        from .. import _CUDA as C
+        self._C = C
+        n = tp.size
+        ms = mc // n
+        self.tp, self.chunks, self.mc, self.ms, self.e, self.device = tp, chunks, mc, ms, e, torch.device(device)
+        stage_bytes = chunks * n * ms * e * 4
+        h8_bytes = chunks * mc * e
+        self.stage_off = 0
+        self.h8_off = (stage_bytes + 255) // 256 * 256
+        self.pad_off = (self.h8_off + h8_bytes + 255) // 256 * 256
+        total = self.pad_off + 256
+        group = tp.group if tp.group is not None else dist.group.WORLD
+        if hasattr(symm, "enable_symm_mem_for_group"):
+            try:
+                symm.enable_symm_mem_for_group(group.group_name)
+            except Exception:  # noqa: BLE001 - newer releases enable it implicitly
+                pass
+        self.buf = symm.empty(total, dtype=torch.uint8, device=self.device)
+        self.handle = symm.rendezvous(self.buf, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.stage = self.buf[:stage_bytes].view(torch.int32).view(chunks, n, ms, e)
+        self.h8 = self.buf[self.h8_off:self.h8_off + h8_bytes].view(torch.int8).view(chunks, mc, e)
+        self.buf[self.pad_off:].zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)  # every rank's pads are zero before the first barrier kernel
+        self.epoch = 0
+        self.pad_ptrs = [p + self.pad_off for p in self.ptrs]
+
+    def scatter_ptrs(self, c):
+        """Where the GEMM epilogue writes row block o of chunk c: slab [my rank] of owner o's stage."""
+        n, ms, e, r = self.tp.size, self.ms, self.e, self.tp.rank
+        return [p + self.stage_off + ((c * n + r) * ms * e) * 4 for p in self.ptrs]
+
+    def q_dst_ptrs(self, c):
+        return [p + self.h8_off + c * self.mc * self.e for p in self.ptrs]
+
+    def barrier(self):
+        self.epoch += 1
+        self._C.tp_barrier(self.pad_ptrs, self.tp.rank, self.epoch, self.device)
