@@ -234,7 +234,8 @@ class OptWorkload:
                 "vocab": self.cfg.vocab_size, "batch": self.batch, "prefill_len": self.seq,
                 "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single GPU",
                 "exchange": ("none" if n_gpus == 1 else
-                             "fused: GEMM-epilogue peer stores -> barrier -> reduce+LayerNorm kernel with peer stores"
+                             (f"peer memory ({self.tp.peer_mode}): partial sums to the owners' slabs -> barrier -> "
+                              "reduce+LayerNorm kernel with peer stores -> barrier")
                              if (self.tp.use_peer_memory and self.tp._workspaces) else
                              "NCCL reduce-scatter / all-gather on a communication stream"),
                 "weights": "random int8 uniform on [-127,127], analytic per-tensor scales x U(0.7,1.3)",

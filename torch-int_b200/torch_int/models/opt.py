@@ -458,7 +458,7 @@ class Int8OPTDecoder(nn.Module):
             if ws is not None:
                 ws.h8[c].copy_(q0.view(mc, e))
                 h8.append(ws.h8[c].view(bc, tgt_len, e))
-                acc.append(None)
+                acc.append(torch.empty((mc, e), dtype=torch.int32, device=dev) if tp.peer_mode == "copy" else None)
             else:
                 h8.append(q0)
                 acc.append(torch.empty((mc, e), dtype=torch.int32, device=dev))
@@ -479,6 +479,8 @@ class Int8OPTDecoder(nn.Module):
             with torch.cuda.stream(comm):
                 comm.wait_event(done[c])
                 if ws is not None:
+                    if tp.peer_mode == "copy":
+                        ws.push_partials(c, acc[c])
                     ws.barrier()
                     res[c] = C.tp_reduce_layernorm_q(ws.stage[c], n, ms * e, scale, bias, res[c], ln.weight,
                                                      ln.bias, ln.eps, ws.q_dst_ptrs(c), rank * ms)
@@ -492,7 +494,7 @@ class Int8OPTDecoder(nn.Module):
         def row_parallel(c, x2d, weight, k):
             """int32 partial sums of a row-parallel linear for chunk c: to the owners' stage slabs
             (peer stores from the GEMM epilogue) or to the local buffer for NCCL."""
-            if ws is not None:
+            if ws is not None and tp.peer_mode != "copy":
                 C.gemm_i8_ex(x2d, weight, None, epilogue=C.EPI_S32_RAW, m=mc, n=e, k=k, lda=k, ldb=k, ldc=e,
                              scatter_ptrs=ws.scatter_ptrs(c), scatter_rows=ms)
             else:

@@ -23,7 +23,8 @@ class TensorParallel:
         self.size = size
         self.rank = rank
         self.group = group
-        self.max_chunks = max_chunks  # pipeline depth of the layer loop (groups of sequences)
+        # pipeline depth of the layer loop (groups of sequences); TI_TP_CHUNKS overrides
+        self.max_chunks = int(os.environ.get("TI_TP_CHUNKS", max_chunks))
         # below this many tokens per group (decode steps, short prompts) the exchanges are latency
         # bound and one all-reduce per exchange point is faster than the pipelined form
         self.min_pipeline_tokens = min_pipeline_tokens
@@ -31,6 +32,10 @@ class TensorParallel:
         self._workspaces = {}
         # fuse the exchanges into the GEMM epilogue / LayerNorm kernel through peer stores
         self.use_peer_memory = os.environ.get("TI_TP_PEER_MEMORY", "1") != "0"
+        # how the partial sums reach their owner: "copy" = local GEMM output, then contiguous peer
+        # copies on the communication stream (copy engines; overlaps all compute of the other groups);
+        # "epilogue" = the GEMM epilogue stores straight into the owners' memory
+        self.peer_mode = os.environ.get("TI_TP_PEER_MODE", "copy")
         # SMs the GEMM grids may use while exchanges overlap them (0 = all); TI_TP_GEMM_SMS overrides
         self.gemm_sm_limit = int(os.environ.get("TI_TP_GEMM_SMS", "0"))
 
@@ -177,6 +182,8 @@ class PeerWorkspace:
         dist.barrier(group=group)  # every rank's pads are zero before the first barrier kernel
         self.epoch = 0
         self.pad_ptrs = [p + self.pad_off for p in self.ptrs]
+        # every rank's stage as a tensor of this process (peer mappings), for contiguous peer copies
+        self.peer_stage = [self.handle.get_buffer(o, (chunks, n, ms, e), torch.int32, 0) for o in range(n)]
 
     def scatter_ptrs(self, c):
         """Where the GEMM epilogue writes row block o of chunk c: slab [my rank] of owner o's stage."""
@@ -185,6 +192,14 @@ class PeerWorkspace:
 
     def q_dst_ptrs(self, c):
         return [p + self.h8_off + c * self.mc * self.e for p in self.ptrs]
+
+    def push_partials(self, c, acc):
+        """Copies row block o of the local partial sums acc [mc, e] into slab [my rank] of owner o's
+        stage, for every o (contiguous device-to-device copies on the current stream)."""
+        r, ms = self.tp.rank, self.ms
+        for i in range(self.tp.size):
+            o = (r + 1 + i) % self.tp.size  # start with the right-hand neighbour: spreads the link load
+            self.peer_stage[o][c, r].copy_(acc[o * ms:(o + 1) * ms], non_blocking=True)
 
     def barrier(self):
         self.epoch += 1
