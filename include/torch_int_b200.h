@@ -92,7 +92,9 @@ enum ti_epilogue {
   TI_EPI_S32_BIAS_S32_SCALE = 4, /* ti_linear_a8_w8_b32_o32_with_scaling */
   TI_EPI_F32_ALPHA = 5,      /* ti_bmm_s8t_s8n_f32t */
   TI_EPI_S8_ALPHA = 6,       /* ti_bmm_s8t_s8n_s8t */
-  TI_EPI_S32_RAW = 7         /* ti_bmm_s8t_s8n_s32t */
+  TI_EPI_S32_RAW = 7,        /* ti_bmm_s8t_s8n_s32t */
+  TI_EPI_S8_BIAS_S8_VEC = 8  /* ti_linear_a8_w8_b8_o8 with per-column alpha[n], beta[n] (alpha_vec, beta_vec):
+                                several such linears that share their input, e.g. q/k/v, run as one GEMM */
 };
 
 /* A [batch2][batch][M][K], B [batch2][batch][N][K], C [batch2][batch][M][N];
@@ -119,6 +121,8 @@ typedef struct ti_gemm_desc {
    * reduce-scatter step of a row-parallel linear fused into the GEMM epilogue. */
   int64_t scatter_rows;
   void* scatter_ptrs[8];
+  const float* alpha_vec; /* TI_EPI_S8_BIAS_S8_VEC only: N per-column alphas, else NULL */
+  const float* beta_vec;  /* TI_EPI_S8_BIAS_S8_VEC only: N per-column betas, else NULL */
 } ti_gemm_desc;
 
 /* The reference has no strided entry point: its wrappers assume packed tensors
@@ -166,12 +170,13 @@ int ti_softmax_q(const float* scores, const float* mask, int8_t* probs, int64_t 
                  int64_t heads, int64_t T, int64_t S, int64_t lds, int64_t ldp, int causal,
                  void* stream);
 
-/* int8 values v [B, T, H, D] (what v_proj produces) -> vt [B, H, D, ld_out], written at columns
- * [col0, col0 + T): the transposed, K-major operand of the P.V product.
+/* int8 values v [B, T, H, D] (what v_proj produces; consecutive tokens ld_in >= H*D elements apart,
+ * so a column block of a wider projection output can be passed) -> vt [B, H, D, ld_out], written at
+ * columns [col0, col0 + T): the transposed, K-major operand of the P.V product.
  * Replaces value_states.transpose(1, 2).contiguous() (torch_int/models/opt.py:180) and lets a
  * pre-allocated cache be filled in place. */
 int ti_transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
-                        int64_t ld_out, int64_t col0, void* stream);
+                        int64_t ld_in, int64_t ld_out, int64_t col0, void* stream);
 
 /* ---- status ---- */
 

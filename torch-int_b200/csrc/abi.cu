@@ -146,6 +146,8 @@ int ti_gemm_i8_ex(const ti_gemm_desc* d, void* stream) {
   g.stride2C = d->stride2C;
   g.alpha = d->alpha;
   g.beta = d->beta;
+  g.alpha_vec = d->alpha_vec;
+  g.beta_vec = d->beta_vec;
   g.epilogue = d->epilogue;
   g.force_bn = d->tile_n;
   g.force_pair = d->cta_pair;
@@ -186,8 +188,8 @@ int ti_softmax_q(const float* scores, const float* mask, int8_t* probs, int64_t 
 }
 
 int ti_transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
-                        int64_t ld_out, int64_t col0, void* stream) {
-  return transpose_values(v, vt, B, T, H, D, ld_out, col0, static_cast<cudaStream_t>(stream));
+                        int64_t ld_in, int64_t ld_out, int64_t col0, void* stream) {
+  return transpose_values(v, vt, B, T, H, D, ld_in, ld_out, col0, static_cast<cudaStream_t>(stream));
 }
 
 const char* ti_last_error(void) { return last_error(); }

@@ -20,6 +20,7 @@ enum Epilogue : int {
   EPI_F32_ALPHA,           // fp32  out = alpha * a
   EPI_S8_ALPHA,            // int8  out = sat_rne(alpha * a)
   EPI_S32_RAW,             // int32 out = acc
+  EPI_S8_BIAS_S8_VEC,      // int8  out = sat_rne(fma(alpha[n], a, beta[n] * f32(bias[n]))): per-column scales
   EPI_COUNT
 };
 
@@ -36,6 +37,8 @@ struct GemmProblem {
   int64_t strideA = 0, strideB = 0, strideC = 0;     // per `batch` index
   int64_t stride2A = 0, stride2B = 0, stride2C = 0;  // per `batch2` index
   float alpha = 1.f, beta = 0.f;
+  const float* alpha_vec = nullptr;  // EPI_S8_BIAS_S8_VEC: N per-column alphas
+  const float* beta_vec = nullptr;   // EPI_S8_BIAS_S8_VEC: N per-column betas
   int epilogue = EPI_S32_RAW;
   int force_bn = 0;    // 0 = choose the N tile automatically
   int force_pair = 0;  // 0 = automatic, 1 = single-CTA tiles only, 2 = CTA-pair tiles (256 x 256)

@@ -50,6 +50,8 @@ struct KernelParams {
   long long ldc, strideC, stride2C;
   long long total_tiles;
   float alpha, beta;
+  const float* alpha_vec;
+  const float* beta_vec;
   int group_m;              // rasterisation: M tiles per column sweep
   int a_b1, a_b2, b_b1, b_b2;  // 0 where an operand is broadcast over a batch index (stride 0), else 1
   // Row-block scatter of the output (tensor-parallel reduce-scatter fused into the epilogue):
@@ -73,7 +75,7 @@ struct Cfg {
   static constexpr int B_BYTES = B_ROWS * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int XPOSE_BYTES = 4 * 32 * 144;       // per epilogue warp: 32 rows x (128 + 16) bytes
-  static constexpr int AUX_BYTES = 2 * BN * 4 + 256 + XPOSE_BYTES;  // bias tiles + barriers + store staging
+  static constexpr int AUX_BYTES = 4 * BN * 4 + 256 + XPOSE_BYTES;  // bias + alpha tiles, barriers, store staging
   static constexpr int STAGES_RAW = (SMEM_BUDGET - 1024 - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES;
@@ -120,10 +122,11 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 template <int EPI>
 struct EpiTraits {
   static constexpr bool kOutS8 =
-      EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU || EPI == EPI_S8_ALPHA;
+      EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU || EPI == EPI_S8_ALPHA || EPI == EPI_S8_BIAS_S8_VEC;
   static constexpr bool kHasBias = EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU ||
                                    EPI == EPI_F32_BIAS_F32 || EPI == EPI_S32_BIAS_S32_ADD ||
-                                   EPI == EPI_S32_BIAS_S32_SCALE;
+                                   EPI == EPI_S32_BIAS_S32_SCALE || EPI == EPI_S8_BIAS_S8_VEC;
+  static constexpr bool kVecAlpha = EPI == EPI_S8_BIAS_S8_VEC;
   static constexpr int kOutBytes = kOutS8 ? 1 : 4;
 };
 
@@ -142,7 +145,7 @@ __device__ __forceinline__ uint32_t epilogue_one(uint32_t acc_bits, uint32_t t, 
     const float a = __int2float_rn(acc);
     float y;
     if constexpr (EPI == EPI_F32_ALPHA || EPI == EPI_S8_ALPHA)
-      y = alpha * a;
+      y = alpha * a;  // (EPI_S8_BIAS_S8_VEC takes the fma branch with its per-column alpha)
     else
       y = __fmaf_rn(alpha, a, __uint_as_float(t));
     if constexpr (EPI == EPI_S8_BIAS_S8_RELU) y = fmaxf(y, 0.f);
@@ -168,8 +171,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* aux = smem + C::STAGES * C::STAGE_BYTES;
   uint32_t* bias_smem = reinterpret_cast<uint32_t*>(aux);  // [2][BN]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aux + 2 * BN * 4);
-  uint8_t* xpose = aux + 2 * BN * 4 + 256;  // [4 warps][32 rows][144 bytes]
+  uint32_t* alpha_smem = bias_smem + 2 * BN;               // [2][BN], per-column alphas (VEC epilogue)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aux + 4 * BN * 4);
+  uint8_t* xpose = aux + 4 * BN * 4 + 256;  // [4 warps][32 rows][144 bytes]
   uint64_t* full_bar = bars;                    // [STAGES]  (PAIR: only the leader's are used)
   uint64_t* empty_bar = bars + C::STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * C::STAGES;   // [2]
@@ -313,7 +317,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int n = n0 + j;
           uint32_t v = 0;
           if (n < p.N) {
-            if constexpr (EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU)
+            if constexpr (EPI == EPI_S8_BIAS_S8_VEC) {
+              v = __float_as_uint(p.beta_vec[n] * static_cast<float>(static_cast<const int8_t*>(p.bias)[n]));
+              alpha_smem[buf * BN + j] = __float_as_uint(p.alpha_vec[n]);
+            } else if constexpr (EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU)
               v = __float_as_uint(p.beta * static_cast<float>(static_cast<const int8_t*>(p.bias)[n]));
             else if constexpr (EPI == EPI_F32_BIAS_F32)
               v = __float_as_uint(p.beta * static_cast<const float*>(p.bias)[n]);
@@ -364,10 +371,16 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int q = 0; q < 8; ++q) {
               uint4 tb = make_uint4(0, 0, 0, 0);
               if constexpr (T::kHasBias) tb = reinterpret_cast<const uint4*>(bs)[c * 8 + q];
-              v[q * 4 + 0] = epilogue_one<EPI>(v[q * 4 + 0], tb.x, p.alpha);
-              v[q * 4 + 1] = epilogue_one<EPI>(v[q * 4 + 1], tb.y, p.alpha);
-              v[q * 4 + 2] = epilogue_one<EPI>(v[q * 4 + 2], tb.z, p.alpha);
-              v[q * 4 + 3] = epilogue_one<EPI>(v[q * 4 + 3], tb.w, p.alpha);
+              float a0 = p.alpha, a1 = p.alpha, a2 = p.alpha, a3 = p.alpha;
+              if constexpr (T::kVecAlpha) {
+                const uint4 ta = reinterpret_cast<const uint4*>(alpha_smem + buf * BN)[c * 8 + q];
+                a0 = __uint_as_float(ta.x); a1 = __uint_as_float(ta.y);
+                a2 = __uint_as_float(ta.z); a3 = __uint_as_float(ta.w);
+              }
+              v[q * 4 + 0] = epilogue_one<EPI>(v[q * 4 + 0], tb.x, a0);
+              v[q * 4 + 1] = epilogue_one<EPI>(v[q * 4 + 1], tb.y, a1);
+              v[q * 4 + 2] = epilogue_one<EPI>(v[q * 4 + 2], tb.z, a2);
+              v[q * 4 + 3] = epilogue_one<EPI>(v[q * 4 + 3], tb.w, a3);
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -570,6 +583,8 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
   p.total_tiles = static_cast<long long>(p.m_tiles) * p.n_tiles * g.batch * g.batch2;
   p.alpha = g.alpha;
   p.beta = g.beta;
+  p.alpha_vec = g.alpha_vec;
+  p.beta_vec = g.beta_vec;
   p.group_m = PAIR ? 8 : 16;
   p.a_b1 = (g.strideA != 0 && g.batch > 1) ? 1 : 0;
   p.a_b2 = (g.stride2A != 0 && g.batch2 > 1) ? 1 : 0;
@@ -683,10 +698,14 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
       }
   }
   const bool out_s8 = g.epilogue == EPI_S8_BIAS_S8 || g.epilogue == EPI_S8_BIAS_S8_RELU ||
-                      g.epilogue == EPI_S8_ALPHA;
+                      g.epilogue == EPI_S8_ALPHA || g.epilogue == EPI_S8_BIAS_S8_VEC;
   const bool has_bias = g.epilogue == EPI_S8_BIAS_S8 || g.epilogue == EPI_S8_BIAS_S8_RELU ||
                         g.epilogue == EPI_F32_BIAS_F32 || g.epilogue == EPI_S32_BIAS_S32_ADD ||
-                        g.epilogue == EPI_S32_BIAS_S32_SCALE;
+                        g.epilogue == EPI_S32_BIAS_S32_SCALE || g.epilogue == EPI_S8_BIAS_S8_VEC;
+  if (g.epilogue == EPI_S8_BIAS_S8_VEC && (!g.alpha_vec || !g.beta_vec)) {
+    set_error("the per-column epilogue needs alpha and beta vectors");
+    return TI_E_INVALID;
+  }
   if (has_bias && !g.bias) {
     set_error("this epilogue needs a bias vector");
     return TI_E_INVALID;
@@ -740,6 +759,7 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
     case EPI_F32_ALPHA: return launch_bn<EPI_F32_ALPHA>(g, bn, pair, stream);
     case EPI_S8_ALPHA: return launch_bn<EPI_S8_ALPHA>(g, bn, pair, stream);
     case EPI_S32_RAW: return launch_bn<EPI_S32_RAW>(g, bn, pair, stream);
+    case EPI_S8_BIAS_S8_VEC: return launch_bn<EPI_S8_BIAS_S8_VEC>(g, bn, pair, stream);
   }
   set_error("unknown epilogue %d", g.epilogue);
   return TI_E_INVALID;

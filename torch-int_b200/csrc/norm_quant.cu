@@ -389,11 +389,11 @@ softmax_q_warp_kernel(const float* __restrict__ scores, const float* __restrict_
 // 4-byte accesses on both sides.
 __global__ void __launch_bounds__(256)
 transpose_values_kernel(const int8_t* __restrict__ v, int8_t* __restrict__ vt, int T, int H, int D,
-                        long long ld_out, int col0) {
+                        long long ld_in, long long ld_out, int col0) {
   __shared__ int8_t tile[64][64 + 4];
   const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
   const int bh = blockIdx.z, b = bh / H, h = bh % H;
-  const int8_t* src = v + ((static_cast<long long>(b) * T) * H + h) * D;  // row t at + t*H*D
+  const int8_t* src = v + static_cast<long long>(b) * T * ld_in + h * D;  // row t at + t*ld_in
   // load: 64 rows (t) x 64 bytes (d); thread -> (row = tid/16 + 16*i, 4-byte column = tid%16)
   const int c4 = threadIdx.x & 15, r = threadIdx.x >> 4;
 #pragma unroll
@@ -401,7 +401,7 @@ transpose_values_kernel(const int8_t* __restrict__ v, int8_t* __restrict__ vt, i
     const int t = t0 + r + 16 * i;
     uint32_t w = 0;
     if (t < T && d0 + 4 * c4 < D)
-      w = *reinterpret_cast<const uint32_t*>(src + static_cast<long long>(t) * H * D + d0 + 4 * c4);
+      w = *reinterpret_cast<const uint32_t*>(src + static_cast<long long>(t) * ld_in + d0 + 4 * c4);
     *reinterpret_cast<uint32_t*>(&tile[r + 16 * i][4 * c4]) = w;
   }
   __syncthreads();
@@ -790,8 +790,8 @@ int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_w
 }
 
 int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
-                     int64_t ld_out, int64_t col0, cudaStream_t stream) {
-  if (B < 0 || T < 0 || H <= 0 || D <= 0 || ld_out < col0 + T || col0 < 0) {
+                     int64_t ld_in, int64_t ld_out, int64_t col0, cudaStream_t stream) {
+  if (B < 0 || T < 0 || H <= 0 || D <= 0 || ld_out < col0 + T || col0 < 0 || ld_in < H * D || ld_in % 4 != 0) {
     set_error("transpose_values: bad shape");
     return TI_E_INVALID;
   }
@@ -809,7 +809,8 @@ int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t 
             static_cast<unsigned>(B * H));
   return check_launch("transpose_values", [&] {
     transpose_values_kernel<<<grid, 256, 0, stream>>>(v, vt, static_cast<int>(T), static_cast<int>(H),
-                                                      static_cast<int>(D), ld_out, static_cast<int>(col0));
+                                                      static_cast<int>(D), ld_in, ld_out,
+                                                      static_cast<int>(col0));
   });
 }
 

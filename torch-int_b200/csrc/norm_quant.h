@@ -28,8 +28,9 @@ int tp_reduce_layernorm_q(const int32_t* stage, int n_partials, int64_t partial_
                           int64_t rows, int64_t H, cudaStream_t stream);
 int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_word, cudaStream_t stream);
 
-// int8 v [B, T, H, D] -> vt [B, H, D, ld_out], written at columns [col0, col0 + T).
+// int8 v [B, T, H, D] (token rows ld_in elements apart) -> vt [B, H, D, ld_out], written at
+// columns [col0, col0 + T).
 int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
-                     int64_t ld_out, int64_t col0, cudaStream_t stream);
+                     int64_t ld_in, int64_t ld_out, int64_t col0, cudaStream_t stream);
 
 }  // namespace ti

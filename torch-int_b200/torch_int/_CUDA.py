@@ -64,6 +64,7 @@ class _GemmDesc(ctypes.Structure):
         ("alpha", _f32), ("beta", _f32),
         ("epilogue", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
         ("scatter_rows", _i64), ("scatter_ptrs", _ptr * 8),
+        ("alpha_vec", _ptr), ("beta_vec", _ptr),
     ]
 
 
@@ -95,7 +96,7 @@ _c_tp_reduce_ln_q = _sig("ti_tp_reduce_layernorm_q",
                           [_ptr, _i32, _i64, _f32, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, ctypes.POINTER(_ptr), _i32,
                            _i64, _i64, _i64, _ptr])
 _c_tp_barrier = _sig("ti_tp_barrier", [ctypes.POINTER(_ptr), _i32, _i32, ctypes.c_uint32, _ptr])
-_c_transpose_values = _sig("ti_transpose_values", [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _ptr])
+_c_transpose_values = _sig("ti_transpose_values", [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr])
 _c_last_error = _sig("ti_last_error", [], ctypes.c_char_p)
 _c_device_status = _sig("ti_device_status", [ctypes.POINTER(ctypes.c_int), _i32])
 _c_abi_version = _sig("ti_abi_version", [])
@@ -105,15 +106,16 @@ if _c_abi_version() != 1:
     raise ImportError("torch_int._CUDA: libtorch_int_b200.so has an unexpected ABI version")
 
 EPI_S8_BIAS_S8, EPI_S8_BIAS_S8_RELU, EPI_F32_BIAS_F32, EPI_S32_BIAS_S32_ADD, \
-    EPI_S32_BIAS_S32_SCALE, EPI_F32_ALPHA, EPI_S8_ALPHA, EPI_S32_RAW = range(8)
+    EPI_S32_BIAS_S32_SCALE, EPI_F32_ALPHA, EPI_S8_ALPHA, EPI_S32_RAW, EPI_S8_BIAS_S8_VEC = range(9)
 _EPI_OUT_DTYPE = {
     EPI_S8_BIAS_S8: torch.int8, EPI_S8_BIAS_S8_RELU: torch.int8, EPI_F32_BIAS_F32: torch.float32,
     EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32,
     EPI_F32_ALPHA: torch.float32, EPI_S8_ALPHA: torch.int8, EPI_S32_RAW: torch.int32,
+    EPI_S8_BIAS_S8_VEC: torch.int8,
 }
 _EPI_BIAS_DTYPE = {
     EPI_S8_BIAS_S8: torch.int8, EPI_S8_BIAS_S8_RELU: torch.int8, EPI_F32_BIAS_F32: torch.float32,
-    EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32,
+    EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32, EPI_S8_BIAS_S8_VEC: torch.int8,
 }
 
 
@@ -365,7 +367,8 @@ def softmax_q(scores, mask=None, num_heads=1, causal=-1):
 
 def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, lda, ldb, ldc,
                stride_a=0, stride_b=0, stride_c=0, stride2_a=0, stride2_b=0, stride2_c=0,
-               alpha=1.0, beta=0.0, tile_n=0, cta_pair=0, scatter_ptrs=None, scatter_rows=0):
+               alpha=1.0, beta=0.0, tile_n=0, cta_pair=0, scatter_ptrs=None, scatter_rows=0,
+               alpha_vec=None, beta_vec=None):
     """Strided form (ti_gemm_i8_ex): operands are addressed through explicit
     element strides starting at each tensor's data pointer, so views can be
     multiplied without contiguous copies.  Writes into `out` and returns it.
@@ -404,6 +407,12 @@ def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, ld
     d.strideA, d.strideB, d.strideC = stride_a, stride_b, stride_c
     d.stride2A, d.stride2B, d.stride2C = stride2_a, stride2_b, stride2_c
     d.alpha, d.beta, d.epilogue, d.tile_n, d.cta_pair = float(alpha), float(beta), epilogue, tile_n, cta_pair
+    if epilogue == EPI_S8_BIAS_S8_VEC:
+        for t, name in ((alpha_vec, "alpha_vec"), (beta_vec, "beta_vec")):
+            if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32 and t.numel() == n
+                    and t.is_contiguous()):
+                raise RuntimeError(f"{name} must be a contiguous CUDA float32 tensor with {n} elements")
+        d.alpha_vec, d.beta_vec = alpha_vec.data_ptr(), beta_vec.data_ptr()
     with _on_device(a.device):
         rc = _c_gemm_ex(ctypes.byref(d), _stream_ptr(a.device))
     _check(rc)
@@ -459,13 +468,20 @@ def tp_barrier(pad_ptrs, rank, epoch, device):
 def transpose_values(v, vt, col0=0):
     """int8 v [B, T, H, D] -> vt [B, H, D, cap] at columns [col0, col0 + T): the transposed
     value layout P.V consumes.  Replaces transpose(1, 2).contiguous() of torch_int/models/opt.py:180."""
-    _require(v, "v", torch.int8, 4)
     _require(vt, "vt", torch.int8, 4)
+    if not (isinstance(v, torch.Tensor) and v.is_cuda and v.dtype == torch.int8 and v.dim() == 4):
+        raise RuntimeError("v must be a 4-dimensional CUDA int8 tensor")
     b, t, h, d = v.shape
+    # v may be a column block of a wider projection output: heads and head_dim contiguous,
+    # tokens `ld_in` apart, sequences t * ld_in apart
+    ld_in = v.stride(1)
+    if v.stride(3) != 1 or v.stride(2) != d or (b > 1 and v.stride(0) != t * ld_in):
+        raise RuntimeError(f"v has unsupported strides {v.stride()} for shape {tuple(v.shape)}")
     if vt.shape[:3] != (b, h, d) or vt.shape[3] < col0 + t or vt.device != v.device:
         raise RuntimeError(f"vt {tuple(vt.shape)} cannot hold v {tuple(v.shape)} at column {col0}")
     with _on_device(v.device):
-        rc = _c_transpose_values(v.data_ptr(), vt.data_ptr(), b, t, h, d, vt.shape[3], col0, _stream_ptr(v.device))
+        rc = _c_transpose_values(v.data_ptr(), vt.data_ptr(), b, t, h, d, ld_in, vt.shape[3], col0,
+                                 _stream_ptr(v.device))
     _check(rc)
     return vt
 

@@ -29,26 +29,18 @@ class StaticInt8KVCache:
     def reset(self):
         self.length = 0
 
-    def append(self, layer_idx, k_proj, v_proj, x2d, bsz, tgt_len, past_len, b0=0):
-        """Projects x2d [B*T, E] to keys and values and stores them at positions
-        [past_len, past_len + T) of the sequences [b0, b0 + B).  The key GEMM writes
-        straight into the cache.  Returns the (keys, transposed values) views of
-        those sequences."""
+    def store(self, layer_idx, k_view, v_view, bsz, tgt_len, past_len, b0=0):
+        """Stores new keys and values at positions [past_len, past_len + T) of the sequences
+        [b0, b0 + B).  k_view / v_view: int8 [B, T, Hl*D] views (tokens may be strided, e.g.
+        column blocks of a fused q/k/v projection).  Returns the (keys, transposed values)
+        views of those sequences."""
         if b0 < 0 or b0 + bsz > self.batch_size:
             raise RuntimeError(f"cache was allocated for batch {self.batch_size}, got sequences [{b0}, {b0 + bsz})")
         if past_len + tgt_len > self.capacity:
             raise RuntimeError(f"cache capacity {self.capacity} exceeded ({past_len} + {tgt_len})")
         kc, vt = self.keys[layer_idx][b0:b0 + bsz], self.values_t[layer_idx][b0:b0 + bsz]
-        el, e = kc.shape[2], x2d.shape[1]
-        dst = kc[:, past_len:, :]  # view starting at the first new row of batch 0
-        if tgt_len == 1:
-            # one row per sequence: a single GEMM with the cache's batch stride as row stride
-            C.gemm_i8_ex(x2d, k_proj.weight, dst, k_proj.bias, epilogue=C.EPI_S8_BIAS_S8, m=bsz, n=el, k=e,
-                         lda=e, ldb=e, ldc=self.capacity * el, alpha=k_proj._scalar("a"), beta=k_proj._scalar("b"))
-        else:
-            C.gemm_i8_ex(x2d, k_proj.weight, dst, k_proj.bias, epilogue=C.EPI_S8_BIAS_S8, m=tgt_len, n=el, k=e,
-                         batch=bsz, lda=e, ldb=e, ldc=el, stride_a=tgt_len * e, stride_b=0,
-                         stride_c=self.capacity * el, alpha=k_proj._scalar("a"), beta=k_proj._scalar("b"))
-        v = v_proj._op(x2d)
-        C.transpose_values(v.view(bsz, tgt_len, self.local_heads, self.head_dim), vt, past_len)
+        kc[:, past_len:past_len + tgt_len].copy_(k_view)
+        C.transpose_values(v_view.as_strided((bsz, tgt_len, self.local_heads, self.head_dim),
+                                             (v_view.stride(0), v_view.stride(1), self.head_dim, 1)),
+                           vt, past_len)
         return kc, vt

@@ -115,22 +115,48 @@ class Int8OPTAttention(nn.Module):
         int8_module.pv_bmm = BMM_S8T_S8N_S8T.from_scale(1.0 / 127, v_output_scale, out_input_scale)
         return int8_module
 
+    def _fused_qkv(self):
+        """Concatenated [3*El, E] weight, [3*El] bias and per-column alpha / beta vectors of the
+        q, k and v projections, for running them as one GEMM.  Built on first use; the three
+        modules' weight buffers are then re-pointed at row blocks of the concatenated tensor, so
+        no second copy of the weights is kept.  Rebuilt if a buffer is replaced or modified."""
+        mods = (self.q_proj, self.k_proj, self.v_proj)
+        key = tuple((m.weight.data_ptr(), m.weight._version, m.bias.data_ptr(), m.bias._version,
+                     m._scalar("a"), m._scalar("b")) for m in mods)
+        hit = getattr(self, "_qkv_cache", None)
+        if hit is not None and hit[0] == key:
+            return hit[1]
+        el = self.local_dim
+        dev = self.q_proj.weight.device
+        w = torch.cat([m.weight for m in mods], dim=0).contiguous()
+        bias = torch.cat([m.bias.reshape(-1) for m in mods], dim=0).contiguous()
+        alpha = torch.cat([torch.full((el,), m._scalar("a"), dtype=torch.float32, device=dev) for m in mods])
+        beta = torch.cat([torch.full((el,), m._scalar("b"), dtype=torch.float32, device=dev) for m in mods])
+        for i, m in enumerate(mods):
+            m.weight = w[i * el:(i + 1) * el]
+            m.bias = bias[i * el:(i + 1) * el].view(1, el)
+        key = tuple((m.weight.data_ptr(), m.weight._version, m.bias.data_ptr(), m.bias._version,
+                     m._scalar("a"), m._scalar("b")) for m in mods)
+        object.__setattr__(self, "_qkv_cache", (key, (w, bias, alpha, beta)))
+        return w, bias, alpha, beta
+
     def _shape(self, tensor: torch.Tensor, seq_len: int, bsz: int):
         return tensor.view(bsz, seq_len, self.local_heads, self.head_dim).transpose(1, 2).contiguous()
 
     # ------------------------------------------------------------------ fast path
-    def attention_core(self, q, k_rows, vt, bsz, tgt_len, src_len, src_pad, k_row_stride, k_batch_stride,
-                       vt_row_stride, causal, mask):
-        """softmax(q k^T) v on strided views.  q [B,T,Hl*D]; k_rows: key rows with
-        row stride `k_row_stride` and batch stride `k_batch_stride`; vt: transposed
-        values [B,Hl,D,*] with row stride `vt_row_stride`.  Returns int8 [B,T,Hl*D]."""
+    def attention_core(self, q, q_row_stride, k_rows, vt, bsz, tgt_len, src_len, src_pad, k_row_stride,
+                       k_batch_stride, vt_row_stride, causal, mask):
+        """softmax(q k^T) v on strided views.  q: query rows [B*T, Hl*D] with row stride
+        `q_row_stride`; k_rows: key rows with row stride `k_row_stride` and batch stride
+        `k_batch_stride`; vt: transposed values [B,Hl,D,*] with row stride `vt_row_stride`.
+        Returns int8 [B,T,Hl*D]."""
         hl, d, el = self.local_heads, self.head_dim, self.local_dim
         dev = q.device
         scores = torch.empty((bsz * hl, tgt_len, src_pad), dtype=torch.float32, device=dev)
         C.gemm_i8_ex(q, k_rows, scores, epilogue=C.EPI_F32_ALPHA, m=tgt_len, n=src_pad, k=d,
-                     batch=hl, batch2=bsz, lda=el, ldb=k_row_stride, ldc=src_pad,
+                     batch=hl, batch2=bsz, lda=q_row_stride, ldb=k_row_stride, ldc=src_pad,
                      stride_a=d, stride_b=d, stride_c=tgt_len * src_pad,
-                     stride2_a=tgt_len * el, stride2_b=k_batch_stride, stride2_c=hl * tgt_len * src_pad,
+                     stride2_a=tgt_len * q_row_stride, stride2_b=k_batch_stride, stride2_c=hl * tgt_len * src_pad,
                      alpha=self.qk_bmm._alpha())
         probs = C.softmax_q(scores, mask, hl, causal=causal)
         del scores
@@ -152,26 +178,32 @@ class Int8OPTAttention(nn.Module):
         bsz, tgt_len, _ = hidden_int8.shape
         hl, d, el = self.local_heads, self.head_dim, self.local_dim
         x2d = hidden_int8.view(-1, self.embed_dim)
-        q = self.q_proj._op(x2d)
+        tokens = x2d.shape[0]
         src_len = past_len + tgt_len
         src_pad = _round_up(src_len, 16)
+        # q, k and v in ONE GEMM over the concatenated weights (per-column alpha / beta); 16 spare
+        # rows at the end keep the padded key reads of the last sequence inside the allocation
+        w, bias, alpha_vec, beta_vec = self._fused_qkv()
+        qkv = torch.empty((tokens + 16, 3 * el), dtype=torch.int8, device=x2d.device)
+        C.gemm_i8_ex(x2d, w, qkv, bias, epilogue=C.EPI_S8_BIAS_S8_VEC, m=tokens, n=3 * el, k=self.embed_dim,
+                     lda=self.embed_dim, ldb=self.embed_dim, ldc=3 * el, alpha_vec=alpha_vec, beta_vec=beta_vec)
+        ld = 3 * el
+        q = qkv[:tokens, :el]
+        k3 = qkv[:tokens].view(bsz, tgt_len, ld)[:, :, el:2 * el]
+        v3 = qkv[:tokens].view(bsz, tgt_len, ld)[:, :, 2 * el:]
         if cache is not None:
-            k_rows, vt = cache.append(layer_idx, self.k_proj, self.v_proj, x2d, bsz, tgt_len, past_len, b0)
+            k_rows, vt = cache.store(layer_idx, k3, v3, bsz, tgt_len, past_len, b0)
             k_row_stride, k_batch_stride, vt_row_stride = el, cache.capacity * el, cache.capacity
         else:
-            k = self.k_proj._op(x2d)
-            v = self.v_proj._op(x2d)
-            k_rows, k_row_stride, k_batch_stride = k, el, tgt_len * el
-            if src_pad != src_len:
-                kp = torch.zeros((bsz, src_pad, el), dtype=torch.int8, device=k.device)
-                kp[:, :src_len] = k.view(bsz, tgt_len, el)
-                k_rows, k_batch_stride = kp, src_pad * el
+            # keys are read in place; rows [T, src_pad) of a sequence are the first rows of the next one
+            # (or the spare rows): finite garbage that the causal limit masks
+            k_rows, k_row_stride, k_batch_stride = qkv[:, el:2 * el], ld, tgt_len * ld
             vt = (torch.zeros if src_pad != src_len else torch.empty)((bsz, hl, d, src_pad), dtype=torch.int8,
-                                                                      device=v.device)
-            C.transpose_values(v.view(bsz, tgt_len, hl, d), vt, 0)
+                                                                      device=x2d.device)
+            C.transpose_values(v3.as_strided((bsz, tgt_len, hl, d), (tgt_len * ld, ld, d, 1)), vt, 0)
             vt_row_stride = src_pad
         causal = past_len if mask is None else -1
-        ctx = self.attention_core(q.view(bsz, tgt_len, el), k_rows, vt, bsz, tgt_len, src_len, src_pad,
+        ctx = self.attention_core(q, ld, k_rows, vt, bsz, tgt_len, src_len, src_pad,
                                   k_row_stride, k_batch_stride, vt_row_stride, causal, mask)
         if context_only:
             return ctx  # int8 [B,T,Hl*D]: the caller runs out_proj itself
