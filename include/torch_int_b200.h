@@ -123,6 +123,15 @@ typedef struct ti_gemm_desc {
   void* scatter_ptrs[8];
   const float* alpha_vec; /* TI_EPI_S8_BIAS_S8_VEC only: N per-column alphas, else NULL */
   const float* beta_vec;  /* TI_EPI_S8_BIAS_S8_VEC only: N per-column betas, else NULL */
+  /* Optional split-K scratch for small-M problems (M <= 128, batch == batch2 == 1, no scatter):
+   * device memory of at least ti_split_k_workspace_bytes(M, N) bytes, 256-byte aligned, all zero
+   * before its first use; every launch leaves it all zero again.  With it, the K dimension of each
+   * output tile is divided over several CTAs, which add int32 partial sums into the scratch; the CTA
+   * that finishes a tile last applies the epilogue.  Launches that share a workspace must not overlap
+   * on the GPU.  NULL: no split-K.  splits: 0 = choose, 1 = off, n = at most n splits. */
+  void* workspace;
+  int64_t workspace_bytes;
+  int32_t splits;
 } ti_gemm_desc;
 
 /* The reference has no strided entry point: its wrappers assume packed tensors
@@ -130,6 +139,9 @@ typedef struct ti_gemm_desc {
  * module makes contiguous copies to satisfy that (torch_int/models/opt.py:80-81,
  * 180,191-196).  This form lets a caller skip those copies. */
 int ti_gemm_i8_ex(const ti_gemm_desc* desc, void* stream);
+
+/* Scratch bytes ti_gemm_desc.workspace must provide for an M x N output. */
+int64_t ti_split_k_workspace_bytes(int64_t M, int64_t N);
 
 /* ---- LayerNorm-quantise ops ---- */
 

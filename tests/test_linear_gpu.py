@@ -152,3 +152,24 @@ def test_rejects_bad_arguments(cuda_ops):
     assert_bit_exact(y, O.linear_a8_w8_b8_o8(x.cpu(), w.cpu(), b.cpu(), 0.01, 0.1))
     # empty batch
     assert C.linear_a8_w8_b8_o8(x[:0], w, b, 1.0, 1.0).shape == (0, 16)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 7168, 7168), (8, 21504, 7168), (16, 1040, 28672), (128, 4096, 4096), (3, 48, 2048)])
+def test_split_k_small_m(cuda_ops, m, n, k):
+    """Few rows, long K (decode steps): K is split over the SMs, partial sums meet in a scratch
+    workspace, the last CTA of a tile applies the epilogue.  Results must not change, twice in a row
+    (the workspace has to come back zeroed)."""
+    C = cuda_ops
+    x, w = rand_s8((m, k), 41), rand_s8((n, k), 42)
+    b8, b32, bf = rand_s8((n,), 43), rand_s32((n,), 44), randn((n,), 45)
+    alpha = 1.0 / (60.0 * k ** 0.5)
+    for _ in range(2):
+        run_all(C, x, w, b8, b32, bf, alpha, 0.01, f"split-K {m}x{n}x{k}")
+    for splits in (1, 2, 5, 16):
+        out = torch.empty((m, n), dtype=torch.int8, device="cuda")
+        C.gemm_i8_ex(x.cuda(), w.cuda(), out, b8.cuda(), epilogue=C.EPI_S8_BIAS_S8, m=m, n=n, k=k,
+                     lda=k, ldb=k, ldc=n, alpha=alpha, beta=0.01, splits=splits)
+        assert_bit_exact(out, O.linear_a8_w8_b8_o8(x, w, b8, alpha, 0.01), f"splits={splits}")
+    ws = C._split_k_workspace(torch.device("cuda", torch.cuda.current_device()))
+    assert int(ws.count_nonzero()) == 0, "the split-K workspace must be left zeroed"
+    assert C.device_status() == 0

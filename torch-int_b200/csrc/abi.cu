@@ -146,6 +146,9 @@ int ti_gemm_i8_ex(const ti_gemm_desc* d, void* stream) {
   g.stride2C = d->stride2C;
   g.alpha = d->alpha;
   g.beta = d->beta;
+  g.ws = d->workspace;
+  g.ws_bytes = d->workspace_bytes;
+  g.splits = d->splits;
   g.alpha_vec = d->alpha_vec;
   g.beta_vec = d->beta_vec;
   g.epilogue = d->epilogue;
@@ -219,6 +222,8 @@ int ti_tp_barrier(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, vo
   }
   return tp_barrier(pads, rank, n, epoch, status, static_cast<cudaStream_t>(stream));
 }
+
+int64_t ti_split_k_workspace_bytes(int64_t M, int64_t N) { return split_k_workspace_bytes(M, N); }
 
 int ti_set_sm_limit(int sms) {
   set_sm_limit(sms);

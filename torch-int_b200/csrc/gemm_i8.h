@@ -44,12 +44,20 @@ struct GemmProblem {
   int force_pair = 0;  // 0 = automatic, 1 = single-CTA tiles only, 2 = CTA-pair tiles (256 x 256)
   // Optional row-block scatter of the output: rows [i*scatter_rows, (i+1)*scatter_rows) are
   // written to scatter_ptrs[i] (row stride ldc) instead of C.  0 = off.
+  // Optional split-K workspace for small-M problems (M <= 128, batch 1): zero-filled on first use,
+  // left zero-filled by every launch; ws_bytes >= split_k_workspace_bytes(M, N).  nullptr: no split-K.
+  void* ws = nullptr;
+  int64_t ws_bytes = 0;
+  int splits = 0;  // 0 = choose; 1 = off; else the number of K splits wanted
   int64_t scatter_rows = 0;
   void* scatter_ptrs[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 // Returns 0 or a negative TI_E_* code (message via set_error()).
 int launch_gemm_i8(const GemmProblem& p, cudaStream_t stream);
+
+// Bytes of split-K workspace a problem with M rows and N columns needs.
+int64_t split_k_workspace_bytes(int64_t M, int64_t N);
 
 // Caps the number of SMs the persistent GEMM grids use (0 = all SMs of the device).
 void set_sm_limit(int sms);

@@ -59,6 +59,12 @@ struct KernelParams {
   // reached by plain peer stores.  scatter_rows == 0: everything goes to C.
   void* scatter[8];
   int scatter_rows;
+  // Split-K (small M): the K blocks of a tile are divided over `splits` work items that add their
+  // int32 partial accumulators into `ws` ([M][N], zero on entry and on exit); the work item that
+  // arrives last at the tile's counter applies the epilogue.  splits == 1: off.
+  int splits, kb_per_split;
+  int32_t* ws;
+  int* counters;
 };
 
 // PAIR = false: one CTA computes a 128 x BN tile (tcgen05 cta_group::1).
@@ -74,7 +80,7 @@ struct Cfg {
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
   static constexpr int B_BYTES = B_ROWS * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int XPOSE_BYTES = 4 * 32 * 144;       // per epilogue warp: 32 rows x (128 + 16) bytes
+  static constexpr int XPOSE_BYTES = 16 + 4 * 32 * 144;  // flag word + per epilogue warp: 32 rows x (128 + 16) bytes
   static constexpr int AUX_BYTES = 4 * BN * 4 + 256 + XPOSE_BYTES;  // bias + alpha tiles, barriers, store staging
   static constexpr int STAGES_RAW = (SMEM_BUDGET - 1024 - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
@@ -88,9 +94,17 @@ struct Cfg {
 
 struct TileCoord {
   int m_tile, n_tile, b1, b2;
+  int kb0, kb1;  // K blocks [kb0, kb1) of this work item
 };
 
 __device__ __forceinline__ TileCoord decode_tile(long long t, const KernelParams& p) {
+  int kb0 = 0, kb1 = p.num_kb;
+  if (p.splits > 1) {
+    const int split = static_cast<int>(t % p.splits);
+    t /= p.splits;
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+  }
   const int per_batch = p.m_tiles * p.n_tiles;
   const long long bidx = t / per_batch;
   int r = static_cast<int>(t - bidx * per_batch);
@@ -106,6 +120,8 @@ __device__ __forceinline__ TileCoord decode_tile(long long t, const KernelParams
   r -= g * group_size;
   c.m_tile = first_m + r % gm;
   c.n_tile = r / gm;
+  c.kb0 = kb0;
+  c.kb1 = kb1;
   return c;
 }
 
@@ -223,7 +239,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const TileCoord tc = decode_tile(t, p);
         const int row_a = tc.m_tile * C::TILE_M + static_cast<int>(rank) * BM;
         const int row_b = tc.n_tile * BN + static_cast<int>(rank) * C::B_ROWS;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, TI_ERR_WAIT_EMPTY);
           if (!ok) break;
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
@@ -263,12 +279,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool ok = true;
       for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
         const int buf = it & 1;
+        int kb0 = 0, kb1 = p.num_kb;
+        if (p.splits > 1) {
+          kb0 = static_cast<int>(t % p.splits) * p.kb_per_split;
+          kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        }
         ok = mbar_wait<PAIR>(smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1, abort_flag,
                              TI_ERR_WAIT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, TI_ERR_WAIT_FULL);
           if (!ok) break;
           tc_fence_after();
@@ -279,7 +300,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // +32 bytes of K inside the 128-byte swizzle row = +2 in the
             // (address >> 4) field of the descriptor.
-            umma_i8<CG>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_i8<CG>(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb != kb0) || (k != 0));
           }
           // Hand the stage back to the producer(s) once these MMAs have read it.
           if constexpr (PAIR) {
@@ -353,6 +374,80 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       };
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       const uint32_t* bs = bias_smem + buf * BN;
+      if (p.splits > 1) {
+        // ---- split-K: add this work item's partial sums into the workspace ----
+        // Rows are transposed through the warp's shared-memory patch so that lane L adds column L of
+        // every valid row: each warp-wide reduction touches 128 contiguous bytes of the workspace.
+        const int valid = min(32, p.M - row0);  // valid rows of this warp (<= 0: none)
+        uint8_t* patch = xpose + 16 + quarter * (32 * 144);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= p.N) break;
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (valid > 0) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(patch + lane * 144 + q * 16) =
+                  make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            __syncwarp();
+            const int col = n0 + c * 32 + lane;
+            if (col < p.N) {
+              int32_t* wcol = p.ws + static_cast<long long>(row0) * p.N + col;
+              for (int r = 0; r < valid; ++r)
+                atomicAdd(wcol + static_cast<long long>(r) * p.N,
+                          *reinterpret_cast<const int*>(patch + r * 144 + lane * 4));
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[buf]));  // the accumulator is drained
+        // ---- the last work item of the tile finishes it ----
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+        if (et == 0) {
+          const int old = atomicAdd(p.counters + tc.n_tile, 1);
+          *reinterpret_cast<volatile int*>(xpose) = (old == p.splits - 1) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+        const bool last = *reinterpret_cast<volatile int*>(xpose) != 0;
+        if (last) {
+          __threadfence();
+          for (int j = et; j < BN; j += EPI_THREADS) {
+            const int col = n0 + j;
+            if (col >= p.N) continue;
+            uint32_t tb = 0;
+            float al = p.alpha;
+            if constexpr (T::kHasBias) tb = bs[j];
+            if constexpr (T::kVecAlpha) al = __uint_as_float(alpha_smem[buf * BN + j]);
+            for (int r0 = 0; r0 < p.M; r0 += 8) {
+              int acc[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i)  // eight independent loads in flight
+                acc[i] = r0 + i < p.M ? __ldcg(p.ws + static_cast<long long>(r0 + i) * p.N + col) : 0;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = r0 + i;
+                if (r >= p.M) break;
+                p.ws[static_cast<long long>(r) * p.N + col] = 0;  // leave the workspace clean
+                const uint32_t o = epilogue_one<EPI>(static_cast<uint32_t>(acc[i]), tb, al);
+                uint8_t* dst =
+                    static_cast<uint8_t*>(p.C) + (static_cast<long long>(r) * p.ldc + col) * T::kOutBytes;
+                if constexpr (T::kOutS8)
+                  *reinterpret_cast<int8_t*>(dst) = static_cast<int8_t>(static_cast<int>(o));
+                else
+                  *reinterpret_cast<uint32_t*>(dst) = o;
+              }
+            }
+          }
+          if (et == 0) p.counters[tc.n_tile] = 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // xpose[0] is reused by the next tile
+        continue;
+      }
       if constexpr (T::kOutS8) {
         // int8 rows: a thread owns one row and writes its 32 bytes of each chunk as two 16-byte stores
         // (one full 32-byte sector).
@@ -399,7 +494,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // 32-bit outputs: the 32 rows x 128 bytes of a chunk are transposed through a per-warp
         // shared-memory patch so that eight lanes write one row's 128 contiguous bytes - full lines
         // for local HBM and efficient packets when the destination is a peer GPU.
-        uint8_t* patch = xpose + quarter * (32 * 144);
+        uint8_t* patch = xpose + 16 + quarter * (32 * 144);
         const int sub = lane >> 3, piece = lane & 7;  // this lane stores piece `piece` of rows sub, sub+4, ...
         uint8_t* rp[8];
 #pragma unroll
@@ -546,8 +641,16 @@ int num_sms() {
   return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
 }
 
+// Split-K workspace layout: one int counter per N tile (sized for the narrowest tile, 256-byte
+// padded), then the [M][N] int32 accumulator.
+int64_t counter_bytes(int bn, int64_t N) {
+  (void)bn;
+  const int64_t tiles = (N + 31) / 32;
+  return (tiles * 4 + 255) / 256 * 256;
+}
+
 template <int BN, int EPI, bool PAIR>
-int launch_one(const GemmProblem& g, cudaStream_t stream) {
+int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
   using C = Cfg<BN, PAIR>;
   static bool attr_done[64] = {false};
   int dev = 0;
@@ -592,6 +695,21 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
   p.b_b2 = (g.stride2B != 0 && g.batch2 > 1) ? 1 : 0;
   p.scatter_rows = static_cast<int>(g.scatter_rows);
   for (int i = 0; i < 8; ++i) p.scatter[i] = g.scatter_rows > 0 ? g.scatter_ptrs[i] : nullptr;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.ws = nullptr;
+  p.counters = nullptr;
+  if (!PAIR && splits > 1) {
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+    if (p.splits > 1) {
+      p.counters = static_cast<int*>(g.ws);
+      p.ws = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(g.ws) + counter_bytes(BN, g.N));
+      p.total_tiles *= p.splits;
+    } else {
+      p.kb_per_split = p.num_kb;
+    }
+  }
   const int sms = num_sms();
   const long long workers = PAIR ? sms / 2 : sms;  // CTAs, or CTA pairs
   const int grid = static_cast<int>(p.total_tiles < workers ? p.total_tiles : workers) * (PAIR ? 2 : 1);
@@ -617,13 +735,13 @@ int launch_one(const GemmProblem& g, cudaStream_t stream) {
 }
 
 template <int EPI>
-int launch_bn(const GemmProblem& g, int bn, bool pair, cudaStream_t stream) {
-  if (pair) return launch_one<256, EPI, true>(g, stream);
+int launch_bn(const GemmProblem& g, int bn, bool pair, int splits, cudaStream_t stream) {
+  if (pair) return launch_one<256, EPI, true>(g, 1, stream);
   switch (bn) {
-    case 256: return launch_one<256, EPI, false>(g, stream);
-    case 128: return launch_one<128, EPI, false>(g, stream);
-    case 64: return launch_one<64, EPI, false>(g, stream);
-    case 32: return launch_one<32, EPI, false>(g, stream);
+    case 256: return launch_one<256, EPI, false>(g, splits, stream);
+    case 128: return launch_one<128, EPI, false>(g, splits, stream);
+    case 64: return launch_one<64, EPI, false>(g, splits, stream);
+    case 32: return launch_one<32, EPI, false>(g, splits, stream);
   }
   set_error("unsupported N tile %d", bn);
   return TI_E_INVALID;
@@ -750,16 +868,55 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
   } else {
     choose_tile(g, &bn, &pair);
   }
+  // Split-K for small M: with one M tile and few N tiles most SMs would idle while a few stream
+  // all of the weights; splitting K puts every SM to work.  Needs a workspace.
+  int splits = 1;
+  if (g.ws != nullptr && !pair && g.M <= BM && g.batch == 1 && g.batch2 == 1 && g.scatter_rows == 0 &&
+      g.splits != 1) {
+    if (g.ws_bytes < split_k_workspace_bytes(g.M, g.N)) {
+      set_error("split-K workspace too small: %lld bytes given, %lld needed", (long long)g.ws_bytes,
+                (long long)split_k_workspace_bytes(g.M, g.N));
+      return TI_E_INVALID;
+    }
+    if ((reinterpret_cast<uintptr_t>(g.ws) & 255) != 0) {
+      set_error("split-K workspace must be 256-byte aligned");
+      return TI_E_INVALID;
+    }
+    const long long num_kb = (g.K + BK - 1) / BK;
+    const int bn_split = g.force_bn ? bn : (g.N >= 4096 ? 128 : 64);
+    const long long tiles = (g.N + bn_split - 1) / bn_split;
+    const long long sms = num_sms();
+    long long max_splits = num_kb / 8 > 0 ? num_kb / 8 : 1;  // at least 8 K blocks per split
+    if (max_splits > 64) max_splits = 64;
+    if (g.splits > 1) {
+      splits = static_cast<int>(g.splits < max_splits ? g.splits : max_splits);
+    } else if (tiles < sms) {
+      // cost in K blocks: (rounds of the persistent grid) x (K blocks per work item), plus a
+      // per-work-item charge for the workspace reduction and the last-CTA epilogue
+      long long best_cost = num_kb * ((tiles + sms - 1) / sms) ;
+      for (long long sp = 2; sp <= max_splits; ++sp) {
+        const long long per = (num_kb + sp - 1) / sp;
+        const long long eff = (num_kb + per - 1) / per;
+        const long long rounds = (tiles * eff + sms - 1) / sms;
+        const long long cost = rounds * (per + 6);
+        if (cost < best_cost) {
+          best_cost = cost;
+          splits = static_cast<int>(eff);
+        }
+      }
+    }
+    if (splits > 1) bn = bn_split;  // otherwise keep the tile the general chooser picked
+  }
   switch (g.epilogue) {
-    case EPI_S8_BIAS_S8: return launch_bn<EPI_S8_BIAS_S8>(g, bn, pair, stream);
-    case EPI_S8_BIAS_S8_RELU: return launch_bn<EPI_S8_BIAS_S8_RELU>(g, bn, pair, stream);
-    case EPI_F32_BIAS_F32: return launch_bn<EPI_F32_BIAS_F32>(g, bn, pair, stream);
-    case EPI_S32_BIAS_S32_ADD: return launch_bn<EPI_S32_BIAS_S32_ADD>(g, bn, pair, stream);
-    case EPI_S32_BIAS_S32_SCALE: return launch_bn<EPI_S32_BIAS_S32_SCALE>(g, bn, pair, stream);
-    case EPI_F32_ALPHA: return launch_bn<EPI_F32_ALPHA>(g, bn, pair, stream);
-    case EPI_S8_ALPHA: return launch_bn<EPI_S8_ALPHA>(g, bn, pair, stream);
-    case EPI_S32_RAW: return launch_bn<EPI_S32_RAW>(g, bn, pair, stream);
-    case EPI_S8_BIAS_S8_VEC: return launch_bn<EPI_S8_BIAS_S8_VEC>(g, bn, pair, stream);
+    case EPI_S8_BIAS_S8: return launch_bn<EPI_S8_BIAS_S8>(g, bn, pair, splits, stream);
+    case EPI_S8_BIAS_S8_RELU: return launch_bn<EPI_S8_BIAS_S8_RELU>(g, bn, pair, splits, stream);
+    case EPI_F32_BIAS_F32: return launch_bn<EPI_F32_BIAS_F32>(g, bn, pair, splits, stream);
+    case EPI_S32_BIAS_S32_ADD: return launch_bn<EPI_S32_BIAS_S32_ADD>(g, bn, pair, splits, stream);
+    case EPI_S32_BIAS_S32_SCALE: return launch_bn<EPI_S32_BIAS_S32_SCALE>(g, bn, pair, splits, stream);
+    case EPI_F32_ALPHA: return launch_bn<EPI_F32_ALPHA>(g, bn, pair, splits, stream);
+    case EPI_S8_ALPHA: return launch_bn<EPI_S8_ALPHA>(g, bn, pair, splits, stream);
+    case EPI_S32_RAW: return launch_bn<EPI_S32_RAW>(g, bn, pair, splits, stream);
+    case EPI_S8_BIAS_S8_VEC: return launch_bn<EPI_S8_BIAS_S8_VEC>(g, bn, pair, splits, stream);
   }
   set_error("unknown epilogue %d", g.epilogue);
   return TI_E_INVALID;
@@ -771,6 +928,8 @@ int* status_word_ptr() {
   if (cudaGetSymbolAddress(&p, ti_kernel_status) != cudaSuccess) return nullptr;
   return static_cast<int*>(p);
 }
+
+int64_t split_k_workspace_bytes(int64_t M, int64_t N) { return counter_bytes(32, N) + M * N * 4; }
 
 void set_sm_limit(int sms) { g_sm_limit = sms > 0 ? sms : 0; }
 

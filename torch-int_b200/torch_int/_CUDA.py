@@ -65,6 +65,7 @@ class _GemmDesc(ctypes.Structure):
         ("epilogue", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("cta_pair", ctypes.c_int32),
         ("scatter_rows", _i64), ("scatter_ptrs", _ptr * 8),
         ("alpha_vec", _ptr), ("beta_vec", _ptr),
+        ("workspace", _ptr), ("workspace_bytes", _i64), ("splits", ctypes.c_int32),
     ]
 
 
@@ -118,6 +119,24 @@ _EPI_BIAS_DTYPE = {
     EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32, EPI_S8_BIAS_S8_VEC: torch.int8,
 }
 
+
+_SPLIT_K_MAX_ROWS = 128            # split-K applies to problems with at most one M tile
+_SPLIT_K_WORKSPACE_BYTES = 32 << 20  # per-device scratch of the split-K path (covers M x N <= 8M)
+_workspaces = {}
+
+
+def _split_k_workspace(device):
+    """Zero-initialised scratch the split-K GEMM path accumulates into (one per device; every
+    launch leaves it zeroed).  Launches that use it must not overlap on the GPU: all of this
+    module's GEMMs of one device are expected on one stream at a time."""
+    ws = _workspaces.get(device.index)
+    if ws is None:
+        ws = torch.zeros(_SPLIT_K_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _workspaces[device.index] = ws
+    return ws
+
+
+split_k = True  # module switch: False disables the split-K path (every GEMM then needs no scratch)
 
 launch_count = 0  # kernels of this library enqueued through this module since import
 
@@ -182,7 +201,7 @@ def _bias_vector(bias, n, dtype, device):
     return bias.reshape(-1).contiguous()
 
 
-def _linear(cfn, x, w, bias, bias_dtype, out_dtype, alpha=None, beta=None):
+def _linear(cfn, epi, x, w, bias, bias_dtype, out_dtype, alpha=None, beta=None):
     _require(x, "input", torch.int8, 2)
     _require(w, "weight", torch.int8, 2)
     if w.device != x.device:
@@ -193,6 +212,10 @@ def _linear(cfn, x, w, bias, bias_dtype, out_dtype, alpha=None, beta=None):
         raise RuntimeError(f"input [{m},{k}] and weight [{n},{kw}] disagree on K")
     b = _bias_vector(bias, n, bias_dtype, x.device)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    if split_k and 0 < m <= _SPLIT_K_MAX_ROWS and k >= 2048:
+        # few rows, long K (decode steps): the strided entry point can split K over the SMs
+        return gemm_i8_ex(x, w, out, b, epilogue=epi, m=m, n=n, k=k, lda=k, ldb=k, ldc=n,
+                          alpha=1.0 if alpha is None else alpha, beta=1.0 if beta is None else beta)
     with _on_device(x.device):
         s = _stream_ptr(x.device)
         if alpha is None:
@@ -207,31 +230,31 @@ def _linear(cfn, x, w, bias, bias_dtype, out_dtype, alpha=None, beta=None):
 def linear_a8_w8_b8_o8(input, weight, bias, alpha, beta):
     """int8 [M,N] = sat_rne(alpha * (input . weight^T) + beta * bias); bias int8.
     Reference: torch_int/kernels/linear.cu:369-473."""
-    return _linear(_c_linear_b8_o8, input, weight, bias, torch.int8, torch.int8, alpha, beta)
+    return _linear(_c_linear_b8_o8, EPI_S8_BIAS_S8, input, weight, bias, torch.int8, torch.int8, alpha, beta)
 
 
 def linear_relu_a8_w8_b8_o8(input, weight, bias, alpha, beta):
     """As linear_a8_w8_b8_o8 with ReLU before rounding.
     Reference: torch_int/kernels/linear.cu:476-625."""
-    return _linear(_c_linear_relu_b8_o8, input, weight, bias, torch.int8, torch.int8, alpha, beta)
+    return _linear(_c_linear_relu_b8_o8, EPI_S8_BIAS_S8_RELU, input, weight, bias, torch.int8, torch.int8, alpha, beta)
 
 
 def linear_a8_w8_bfp32_ofp32(input, weight, bias, alpha, beta):
     """fp32 [M,N] = alpha * (input . weight^T) + beta * bias; bias fp32.
     Reference: torch_int/kernels/linear.cu:246-365."""
-    return _linear(_c_linear_bfp32_ofp32, input, weight, bias, torch.float32, torch.float32, alpha, beta)
+    return _linear(_c_linear_bfp32_ofp32, EPI_F32_BIAS_F32, input, weight, bias, torch.float32, torch.float32, alpha, beta)
 
 
 def linear_a8_w8_b32_o32(input, weight, bias):
     """int32 [M,N] = input . weight^T + bias; bias int32.
     Reference: torch_int/kernels/linear.cu:13-136."""
-    return _linear(_c_linear_b32_o32, input, weight, bias, torch.int32, torch.int32)
+    return _linear(_c_linear_b32_o32, EPI_S32_BIAS_S32_ADD, input, weight, bias, torch.int32, torch.int32)
 
 
 def linear_a8_w8_b32_o32_with_scaling(input, weight, bias, alpha, beta):
     """int32 [M,N] = sat_rne(alpha * (input . weight^T) + beta * bias); bias int32.
     Reference: torch_int/kernels/linear.cu:139-243."""
-    return _linear(_c_linear_b32_o32_scaling, input, weight, bias, torch.int32, torch.int32, alpha, beta)
+    return _linear(_c_linear_b32_o32_scaling, EPI_S32_BIAS_S32_SCALE, input, weight, bias, torch.int32, torch.int32, alpha, beta)
 
 
 def _bmm(cfn, a, b, out_dtype, alpha=None):
@@ -368,7 +391,7 @@ def softmax_q(scores, mask=None, num_heads=1, causal=-1):
 def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, lda, ldb, ldc,
                stride_a=0, stride_b=0, stride_c=0, stride2_a=0, stride2_b=0, stride2_c=0,
                alpha=1.0, beta=0.0, tile_n=0, cta_pair=0, scatter_ptrs=None, scatter_rows=0,
-               alpha_vec=None, beta_vec=None):
+               alpha_vec=None, beta_vec=None, splits=0):
     """Strided form (ti_gemm_i8_ex): operands are addressed through explicit
     element strides starting at each tensor's data pointer, so views can be
     multiplied without contiguous copies.  Writes into `out` and returns it.
@@ -413,6 +436,12 @@ def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, ld
                     and t.is_contiguous()):
                 raise RuntimeError(f"{name} must be a contiguous CUDA float32 tensor with {n} elements")
         d.alpha_vec, d.beta_vec = alpha_vec.data_ptr(), beta_vec.data_ptr()
+    if split_k and m <= _SPLIT_K_MAX_ROWS and batch == 1 and batch2 == 1 and k >= 2048 \
+            and 256 + m * n * 4 + n // 8 <= _SPLIT_K_WORKSPACE_BYTES:
+        ws = _split_k_workspace(a.device)
+        d.workspace, d.workspace_bytes, d.splits = ws.data_ptr(), ws.numel(), splits
+    else:
+        d.workspace, d.workspace_bytes, d.splits = None, 0, 1
     with _on_device(a.device):
         rc = _c_gemm_ex(ctypes.byref(d), _stream_ptr(a.device))
     _check(rc)
