@@ -64,6 +64,23 @@ int ti_linear_a8_w8_b32_o32_with_scaling(const int8_t* input, const int8_t* weig
                                          const int32_t* bias, int32_t* out, int64_t M, int64_t N,
                                          int64_t K, float alpha, float beta, void* stream);
 
+/* Same result as ti_linear_a8_w8_b8_o8 for M <= 128 rows, for callers that may not allocate device
+ * memory (an inference server that owns the whole GPU and gives plug-ins no allocator, a serving loop
+ * where cudaMalloc's implicit synchronisation is banned after start-up, code running after the
+ * framework's allocator was frozen).  The split-K scratch such small problems want is a 4 MiB array
+ * built into the library (held by every GPU that loads it until exit); nothing is allocated, here or
+ * by any library this calls.  Refused with an error: M > 128, or ti_split_k_workspace_bytes(M, N) >
+ * 4 MiB (e.g. M = 16 allows N up to 65024).  The array is shared by all calls and keeps the last
+ * call's contents: the kernel re-zeroes what it used, so back-to-back calls on one stream are fine, but
+ * calls that overlap on the GPU race on it - serialise them.  The first call on each device resolves
+ * the array's device address (cudaGetSymbolAddress, with that device current); make that first call
+ * before starting any stream capture.
+ * No counterpart in the reference, which allocates a fresh output and workspace in every call
+ * (torch_int/kernels/linear.cu:420,450). */
+int ti_linear_a8_w8_b8_o8_static(const int8_t* input, const int8_t* weight, const int8_t* bias,
+                                 int8_t* out, int64_t M, int64_t N, int64_t K, float alpha, float beta,
+                                 void* stream);
+
 /* ---- batched products: C[b] = epilogue(A[b][M,K] . B[b][N,K]^T), packed tensors ---- */
 
 /* fp32 C = alpha * float(acc).

@@ -955,6 +955,118 @@ int device_status(int* status, bool reset) {
   return TI_OK;
 }
 
+// ------------------------------------------------- entry point that allocates nothing
+//
+// ti_linear_a8_w8_b8_o8_static: the int8-output linear for few rows (decode steps) with its
+// split-K scratch taken from a fixed array inside this library instead of from the caller.
+//
+// Who needs this: hosts that are not allowed to allocate device memory when they call us.
+// Examples are an inference server that reserves the whole GPU up front and hands plug-ins no
+// allocator; a latency-critical serving loop in which cudaMalloc (an implicit device
+// synchronisation) is banned after start-up; and code that runs after the framework's
+// caching allocator has been frozen.  Such a caller cannot provide ti_gemm_desc.workspace,
+// yet without split-K a 16-row problem keeps most SMs idle.  So the scratch lives here, as a
+// file-scope device array: every GPU that loads this library holds its kStaticScratchBytes
+// (4 MiB) until the process exits, whether or not the entry point is ever called.
+//
+// Rules that follow from sharing one array:
+//   * sizes whose scratch need (ti_split_k_workspace_bytes(M, N)) exceeds the array, or
+//     M > 128, are refused with an error - nothing is allocated as a fallback;
+//   * the array keeps whatever the last call left in it.  The split-K kernel needs it all zero
+//     on entry and restores every word it touched to zero before it ends, and the array starts
+//     zeroed when the library is loaded, so consecutive calls on one stream are safe;
+//   * two calls that overlap on the GPU (different streams, or different host threads feeding
+//     different streams) would add into the same words: do not do that - serialise them;
+//   * the array's name is only a host-side handle; the device address is looked up with
+//     cudaGetSymbolAddress the first time the entry point runs on a device (with that device
+//     current) and cached.  Make that first call before any stream capture begins.
+namespace {
+constexpr long long kStaticScratchBytes = 4ll << 20;
+}
+static __device__ __align__(256) unsigned char ti_static_scratch[kStaticScratchBytes];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[64] = {nullptr};
+
+// Device address of ti_static_scratch on the current device (set up once per device).
+int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("ti_linear_a8_w8_b8_o8_static: cannot identify the current device");
+    return TI_E_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), ti_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      set_error("ti_linear_a8_w8_b8_o8_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return TI_E_CUDA;
+    }
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return TI_OK;
+}
+}  // namespace
+
+}  // namespace ti
+
+#pragma GCC visibility push(default)
+extern "C" int ti_linear_a8_w8_b8_o8_static(const int8_t* input, const int8_t* weight, const int8_t* bias,
+                                            int8_t* out, int64_t M, int64_t N, int64_t K, float alpha,
+                                            float beta, void* stream) {
+  using namespace ti;
+  if (M < 0 || N < 0 || K < 0) {
+    set_error("ti_linear_a8_w8_b8_o8_static: negative dimension");
+    return TI_E_INVALID;
+  }
+  if (M > 128) {
+    set_error("ti_linear_a8_w8_b8_o8_static: M=%lld exceeds the 128 rows this entry point handles "
+              "(use ti_linear_a8_w8_b8_o8, which needs no scratch for large M)", (long long)M);
+    return TI_E_INVALID;
+  }
+  const long long need = split_k_workspace_bytes(M, N);
+  if (need > kStaticScratchBytes) {
+    set_error("ti_linear_a8_w8_b8_o8_static: M=%lld x N=%lld needs %lld bytes of scratch, the built-in array "
+              "holds %lld; nothing is allocated as a fallback",
+              (long long)M, (long long)N, need, kStaticScratchBytes);
+    return TI_E_INVALID;
+  }
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != TI_OK) return rc;
+  GemmProblem g;
+  g.A = input;
+  g.B = weight;
+  g.C = out;
+  g.bias = bias;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.lda = K;
+  g.ldb = K;
+  g.ldc = N;
+  g.strideA = M * K;
+  g.strideB = N * K;
+  g.strideC = M * N;
+  g.stride2A = g.strideA;
+  g.stride2B = g.strideB;
+  g.stride2C = g.strideC;
+  g.alpha = alpha;
+  g.beta = beta;
+  g.epilogue = EPI_S8_BIAS_S8;
+  g.ws = scratch;  // the looked-up device address, never the symbol itself
+  g.ws_bytes = kStaticScratchBytes;
+  g.splits = 0;
+  return launch_gemm_i8(g, static_cast<cudaStream_t>(stream));
+}
+#pragma GCC visibility pop
+
+namespace ti {
+
 // ------------------------------------------------------------ error plumbing
 namespace {
 thread_local char g_err[512] = "";
