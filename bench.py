@@ -274,26 +274,41 @@ class OptWorkload:
                 "step_frac_of_peak": round(step_ops / (ms * 1e-3) / 1e12 / peak, 4)}
 
     def decode_rate(self, steps=None):
-        """Greedy decoding with the static int8 cache after the prefill: tokens/s over `steps` steps."""
+        """Greedy decoding with the static int8 cache after the prefill: tokens/s over `steps` one-token
+        steps (one CUDA-graph replay per step on a single GPU; eager launches under tensor parallelism)."""
         steps = steps or self.decode_steps
-        cache = self.model.new_cache(self.batch, self.seq + steps + 1)
-        out = self.model(self.ids, past_key_values=cache, use_cache=True, last_token_only=True)
+        model = self.model
+        cache = model.new_cache(self.batch, self.seq + steps + 8)
+        out = model(self.ids, past_key_values=cache, use_cache=True, last_token_only=True)
         nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
         for _ in range(3):
-            out = self.model(nxt, past_key_values=cache, use_cache=True, last_token_only=True)
-            nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+            nxt = model.decode_step(nxt, cache).argmax(dim=-1, keepdim=True)
+        graph = None
+        if self.world == 1:
+            static_tok = nxt.clone()
+            length = cache.length
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_next = model.decode_step(static_tok, cache).argmax(dim=-1, keepdim=True)
+            cache.length = length
         torch.cuda.synchronize()
+        c0 = self.C.launch_count
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps - 3):
-            out = self.model(nxt, past_key_values=cache, use_cache=True, last_token_only=True)
-            nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+            if graph is not None:
+                static_tok.copy_(nxt)
+                graph.replay()
+                nxt = static_next.clone()
+            else:
+                nxt = model.decode_step(nxt, cache).argmax(dim=-1, keepdim=True)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / (steps - 3)
-        wbytes = sum(b.numel() for n, b in self.model.named_buffers() if b.dtype == torch.int8)
+        wbytes = sum(b.numel() for n, b in model.named_buffers() if b.dtype == torch.int8)
         return {"decode_tokens_per_s": round(self.batch / (ms * 1e-3), 1), "decode_ms_per_step": round(ms, 3),
-                "decode_steps_timed": steps - 3, "decode_weight_gb_per_s_per_gpu": round(wbytes / (ms * 1e-3) / 1e9, 1)}
+                "decode_steps_timed": steps - 3, "decode_weight_gb_per_s_per_gpu": round(wbytes / (ms * 1e-3) / 1e9, 1),
+                "decode_mode": "CUDA graph replay" if graph is not None else "eager launches"}
 
     def cpu_sample(self):
         return opt_cpu_sample(self.arch, self.batch, self.seq)

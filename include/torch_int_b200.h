@@ -207,6 +207,22 @@ int ti_softmax_q(const float* scores, const float* mask, int8_t* probs, int64_t 
 int ti_transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
                         int64_t ld_in, int64_t ld_out, int64_t col0, void* stream);
 
+/* Attention of ONE new token per sequence over the int8 key/value cache, in one kernel: appends the
+ * token's key row and value column at position *position, then
+ *   s_j = alpha_qk * float(q . k_j),  p = int8(rne(127 * softmax(s))),  ctx = sat_rne(alpha_pv * float(p . v))
+ * over positions 0 .. *position.  qkv [batch, >= 3*E] holds the token's q | k | v (E = local_heads *
+ * head_dim, head_dim 64 or 128); keys [batch, capacity, E]; values_t [batch, local_heads, head_dim,
+ * capacity]; ctx [batch, E] with row stride ld_ctx.  `position` is DEVICE memory (tokens already cached,
+ * the same for all sequences), so the call has no per-step host parameters and a decode step can be
+ * captured in a CUDA graph; ti_advance_position adds to it on the stream.  A full cache sets the status
+ * word of ti_device_status to 201 and writes nothing.
+ * Replaces, for tgt_len == 1, the torch.cat cache update, bmm_s8t_s8n_f32t, the softmax chain, the value
+ * transpose and bmm_s8t_s8n_s8t of Int8OPTAttention.forward (torch_int/models/opt.py:113-116,131-181). */
+int ti_decode_attention_s8(const int8_t* qkv, int64_t ld_qkv, int8_t* keys, int8_t* values_t, int64_t batch,
+                           int64_t local_heads, int64_t head_dim, int64_t capacity, const int32_t* position,
+                           float alpha_qk, float alpha_pv, int8_t* ctx, int64_t ld_ctx, void* stream);
+int ti_advance_position(int32_t* position, int32_t by, void* stream);
+
 /* ---- status ---- */
 
 /* Message of the last error raised on the calling thread ("" if none). */

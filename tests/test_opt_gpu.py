@@ -152,3 +152,49 @@ def test_static_cache_decode_matches_recompute(cuda_ops):
     want, _ = OM.causal_lm_logits(sd, cfg, out[:, :-1].cpu())
     assert float((want[:, 20:, :].argmax(-1) == out[:, 21:].cpu()).double().mean()) >= 0.8
     assert cuda_ops.device_status() == 0
+
+
+@pytest.mark.parametrize("bsz,heads,d,length", [(2, 3, 128, 0), (3, 2, 128, 37), (1, 4, 64, 200), (2, 2, 128, 1023)])
+def test_decode_attention_kernel(cuda_ops, bsz, heads, d, length):
+    """The one-token attention kernel against the op chain it replaces (bmm_s8t_s8n_f32t -> softmax ->
+    x127 -> round -> bmm_s8t_s8n_s8t on the oracle), including the cache append at a device-side position."""
+    C = cuda_ops
+    e, cap = heads * d, 1024
+    g = torch.Generator().manual_seed(3)
+    keys = torch.randint(-127, 128, (bsz, cap, e), generator=g, dtype=torch.int8)
+    vals = torch.randint(-127, 128, (bsz, heads, d, cap), generator=g, dtype=torch.int8)
+    qkv = torch.randint(-60, 61, (bsz + 16, 3 * e), generator=g, dtype=torch.int8)
+    a_qk, a_pv = 1.5 / (35.0 * 73.0 * d ** 0.5), 0.02
+    kd, vd = keys.cuda(), vals.cuda()
+    pos = torch.full((1,), length, dtype=torch.int32, device="cuda")
+    ctx = C.decode_attention(qkv.cuda(), kd, vd, pos, a_qk, a_pv)
+    # the cache received the new key row and value column
+    assert torch.equal(kd[:, length].cpu(), qkv[:bsz, e:2 * e])
+    assert torch.equal(vd[..., length].cpu(), qkv[:bsz, 2 * e:].view(bsz, heads, d))
+    keys[:, length] = qkv[:bsz, e:2 * e]
+    vals[..., length] = qkv[:bsz, 2 * e:].view(bsz, heads, d)
+    assert torch.equal(kd.cpu(), keys) and torch.equal(vd.cpu(), vals), "nothing else in the cache may change"
+    s = length + 1
+    q = qkv[:bsz, :e].view(bsz, 1, heads, d).transpose(1, 2).reshape(bsz * heads, 1, d).contiguous()
+    k = keys[:, :s].view(bsz, s, heads, d).transpose(1, 2).reshape(bsz * heads, s, d).contiguous()
+    probs = O.softmax_q(O.bmm_s8t_s8n_f32t(q, k, a_qk))
+    vt = vals[..., :s].reshape(bsz * heads, d, s).contiguous()
+    want = O.bmm_s8t_s8n_s8t(probs, vt, a_pv).view(bsz, heads * d)
+    diff = (ctx.cpu().int() - want.int()).abs()
+    assert int(diff.max()) <= 2 and float((diff == 0).double().mean()) > 0.97, (int(diff.max()), float((diff == 0).double().mean()))
+    C.advance_position(pos, 1)
+    assert int(pos.item()) == length + 1
+    assert C.device_status() == 0
+
+
+def test_generate_with_and_without_cuda_graph(cuda_ops):
+    cfg, model = small_model()
+    g = torch.Generator().manual_seed(13)
+    prompt = torch.randint(0, cfg.vocab_size, (3, 19), generator=g).cuda()
+    eager = model.generate_greedy(prompt, 12, use_cuda_graph=False)
+    cache = model.new_cache(3, 64)
+    graphed = model.generate_greedy(prompt, 12, cache=cache, use_cuda_graph=True)
+    again = model.generate_greedy(prompt, 12, cache=cache, use_cuda_graph=True)  # replays the stored graph
+    assert torch.equal(eager, graphed) and torch.equal(graphed, again)
+    assert cache.length == 19 + 11 and int(cache.pos.item()) == cache.length
+    assert cuda_ops.device_status() == 0

@@ -195,6 +195,17 @@ int ti_transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64
   return transpose_values(v, vt, B, T, H, D, ld_in, ld_out, col0, static_cast<cudaStream_t>(stream));
 }
 
+int ti_decode_attention_s8(const int8_t* qkv, int64_t ld_qkv, int8_t* keys, int8_t* values_t, int64_t batch,
+                           int64_t local_heads, int64_t head_dim, int64_t capacity, const int32_t* position,
+                           float alpha_qk, float alpha_pv, int8_t* ctx, int64_t ld_ctx, void* stream) {
+  return decode_attention_s8(qkv, ld_qkv, keys, values_t, batch, local_heads, head_dim, capacity, position,
+                             alpha_qk, alpha_pv, ctx, ld_ctx, static_cast<cudaStream_t>(stream));
+}
+
+int ti_advance_position(int32_t* position, int32_t by, void* stream) {
+  return advance_position(position, by, static_cast<cudaStream_t>(stream));
+}
+
 const char* ti_last_error(void) { return last_error(); }
 
 int ti_device_status(int* status, int reset) {

@@ -1,0 +1,204 @@
+// One-token (decode step) attention over the int8 key/value cache, one kernel per layer:
+//   append the new key row and value column at position *pos,
+//   s_j = alpha_qk * float(q . k_j)                      j = 0 .. *pos          (int8 dot products)
+//   p_j = int8(rne(127 * softmax(s)_j))
+//   ctx = int8(sat_rne(alpha_pv * float(sum_j p_j * v_j)))
+// i.e. what bmm_s8t_s8n_f32t -> softmax -> *127 -> round -> bmm_s8t_s8n_s8t compute for a single
+// query row (torch_int/models/opt.py:131-181), with the same arithmetic as those ops' kernels.
+// The position is read from DEVICE memory, so the launch has no per-step host parameters and a
+// whole decode step can be captured in a CUDA graph and replayed.
+//
+// Layouts (those of the static cache): keys [B, cap, Hl*D] rows; values transposed
+// [B, Hl, D, cap]; qkv [B, 3*Hl*D] = the fused projection output of the new token.
+// One CTA of 128 threads per (sequence, head); HBM-bound on the cache: (D + D) * (*pos + 1) bytes.
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "gemm_i8.h"
+#include "norm_quant.h"
+
+namespace ti {
+namespace {
+
+__device__ __forceinline__ int dot16(const uint4& a, const uint4& b, int acc) {
+  acc = __dp4a(static_cast<int>(a.x), static_cast<int>(b.x), acc);
+  acc = __dp4a(static_cast<int>(a.y), static_cast<int>(b.y), acc);
+  acc = __dp4a(static_cast<int>(a.z), static_cast<int>(b.z), acc);
+  acc = __dp4a(static_cast<int>(a.w), static_cast<int>(b.w), acc);
+  return acc;
+}
+
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int D>
+__global__ void __launch_bounds__(128)
+decode_attention_s8_kernel(const int8_t* __restrict__ qkv, long long ld_qkv, int8_t* __restrict__ keys,
+                           int8_t* __restrict__ values_t, int cap, int hl, const int* __restrict__ pos,
+                           float alpha_qk, float alpha_pv, int8_t* __restrict__ ctx, long long ld_ctx,
+                           int* status) {
+  extern __shared__ __align__(16) unsigned char dsm[];
+  float* s_scores = reinterpret_cast<float*>(dsm);                 // [cap]
+  int8_t* s_probs = reinterpret_cast<int8_t*>(dsm + cap * 4);      // [cap] (zero beyond the length)
+  __shared__ float red[8];
+  const int b = blockIdx.x / hl, h = blockIdx.x % hl;
+  const int el = hl * D;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int len = *pos;  // keys/values already cached; the new token goes to position `len`
+  if (len < 0 || len >= cap) {
+    if (tid == 0) atomicCAS(status, 0, 201);  // cache full: refuse instead of writing out of bounds
+    return;
+  }
+  const int S = len + 1;
+  const int8_t* qrow = qkv + b * ld_qkv + h * D;
+  int8_t* krows = keys + (static_cast<long long>(b) * cap) * el + h * D;   // row j at + j*el
+  int8_t* vrows = values_t + (static_cast<long long>(b) * hl + h) * D * static_cast<long long>(cap);
+
+  // append the new key row (D bytes) and value column (one byte in each of D rows)
+  if (tid < D / 16)
+    reinterpret_cast<uint4*>(krows + static_cast<long long>(len) * el)[tid] =
+        reinterpret_cast<const uint4*>(qrow + el)[tid];
+  if (tid < D) vrows[static_cast<long long>(tid) * cap + len] = qrow[2 * el + tid];
+
+  // q in registers
+  uint4 q[D / 16];
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i) q[i] = reinterpret_cast<const uint4*>(qrow)[i];
+  __syncthreads();  // the new key row is visible to the whole CTA
+
+  // scores: thread t takes rows t, t+128, ...
+  float mx = -FLT_MAX;
+  for (int j = tid; j < S; j += 128) {
+    const uint4* kr = reinterpret_cast<const uint4*>(krows + static_cast<long long>(j) * el);
+    int acc = 0;
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) acc = dot16(q[i], kr[i], acc);
+    const float s = alpha_qk * __int2float_rn(acc);
+    s_scores[j] = s;
+    mx = fmaxf(mx, s);
+  }
+  mx = warp_max_f(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  float sum = 0.f;
+  for (int j = tid; j < S; j += 128) {
+    const float e = expf(s_scores[j] - mx);
+    s_scores[j] = e;
+    sum += e;
+  }
+  sum = warp_sum_f(sum);
+  __syncthreads();  // red[] reads above are done
+  if (lane == 0) red[4 + warp] = sum;
+  __syncthreads();
+  sum = (red[4] + red[5]) + (red[6] + red[7]);
+  const int s_pad = (S + 15) & ~15;
+  for (int j = tid; j < s_pad; j += 128) {
+    int p = 0;
+    if (j < S) p = max(-128, min(127, __float2int_rn(__fdiv_rn(s_scores[j], sum) * 127.f)));
+    s_probs[j] = static_cast<int8_t>(p);
+  }
+  __syncthreads();
+
+  // context: warp w owns value rows d = w*(D/4) .. ; lanes stride over the positions 16 bytes at a time
+  for (int i = 0; i < D / 4; ++i) {
+    const int d = warp * (D / 4) + i;
+    const int8_t* vr = vrows + static_cast<long long>(d) * cap;
+    int acc = 0;
+    for (int j = lane * 16; j < s_pad; j += 512)
+      acc = dot16(*reinterpret_cast<const uint4*>(s_probs + j), *reinterpret_cast<const uint4*>(vr + j), acc);
+    acc = warp_sum_i(acc);
+    if (lane == 0) {
+      const int o = max(-128, min(127, __float2int_rn(alpha_pv * __int2float_rn(acc))));
+      ctx[b * ld_ctx + h * D + d] = static_cast<int8_t>(o);
+    }
+  }
+}
+
+__global__ void advance_position_kernel(int* pos, int by) { *pos += by; }
+
+}  // namespace
+
+int decode_attention_s8(const int8_t* qkv, int64_t ld_qkv, int8_t* keys, int8_t* values_t, int64_t batch,
+                        int64_t local_heads, int64_t head_dim, int64_t cap, const int* pos, float alpha_qk,
+                        float alpha_pv, int8_t* ctx, int64_t ld_ctx, cudaStream_t stream) {
+  if (batch < 0 || local_heads <= 0 || cap <= 0 || cap % 16 != 0 || (head_dim != 128 && head_dim != 64)) {
+    set_error("decode_attention_s8: head_dim must be 64 or 128 and the cache capacity a positive multiple of 16");
+    return TI_E_INVALID;
+  }
+  if (batch == 0) return TI_OK;
+  if (!qkv || !keys || !values_t || !pos || !ctx) {
+    set_error("decode_attention_s8: null pointer");
+    return TI_E_INVALID;
+  }
+  const int64_t el = local_heads * head_dim;
+  if (ld_qkv < 3 * el || ld_qkv % 16 != 0 || ld_ctx < el ||
+      ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(keys) |
+        reinterpret_cast<uintptr_t>(values_t)) & 15) != 0) {
+    set_error("decode_attention_s8: rows must be 16-byte aligned and hold q, k and v side by side");
+    return TI_E_INVALID;
+  }
+  const size_t smem = static_cast<size_t>(cap) * 5;
+  if (smem > 200 * 1024 || batch * local_heads > 0x7FFFFFFF) {
+    set_error("decode_attention_s8: cache capacity %lld too large", (long long)cap);
+    return TI_E_INVALID;
+  }
+  int* status = status_word_ptr();
+  if (!status) {
+    set_error("decode_attention_s8: cannot resolve the device status word");
+    return TI_E_CUDA;
+  }
+  const unsigned grid = static_cast<unsigned>(batch * local_heads);
+  cudaError_t e;
+  if (head_dim == 128) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(decode_attention_s8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem));
+    decode_attention_s8_kernel<128><<<grid, 128, smem, stream>>>(
+        qkv, ld_qkv, keys, values_t, static_cast<int>(cap), static_cast<int>(local_heads), pos, alpha_qk,
+        alpha_pv, ctx, ld_ctx, status);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(decode_attention_s8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem));
+    decode_attention_s8_kernel<64><<<grid, 128, smem, stream>>>(
+        qkv, ld_qkv, keys, values_t, static_cast<int>(cap), static_cast<int>(local_heads), pos, alpha_qk,
+        alpha_pv, ctx, ld_ctx, status);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("decode_attention_s8 launch failed: %s", cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  return TI_OK;
+}
+
+int advance_position(int* pos, int by, cudaStream_t stream) {
+  if (!pos) {
+    set_error("advance_position: null pointer");
+    return TI_E_INVALID;
+  }
+  advance_position_kernel<<<1, 1, 0, stream>>>(pos, by);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("advance_position launch failed: %s", cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  return TI_OK;
+}
+
+}  // namespace ti

@@ -924,9 +924,15 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
 
 // Device address of the status word, for kernels of other translation units.
 int* status_word_ptr() {
-  void* p = nullptr;
-  if (cudaGetSymbolAddress(&p, ti_kernel_status) != cudaSuccess) return nullptr;
-  return static_cast<int*>(p);
+  static int* cached[64] = {nullptr};  // resolved once per device (not during stream capture)
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, ti_kernel_status) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
 }
 
 int64_t split_k_workspace_bytes(int64_t M, int64_t N) { return counter_bytes(32, N) + M * N * 4; }

@@ -33,4 +33,11 @@ int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_w
 int transpose_values(const int8_t* v, int8_t* vt, int64_t B, int64_t T, int64_t H, int64_t D,
                      int64_t ld_in, int64_t ld_out, int64_t col0, cudaStream_t stream);
 
+// One-token attention over the int8 cache with the position read from device memory
+// (decode_attention.cu).
+int decode_attention_s8(const int8_t* qkv, int64_t ld_qkv, int8_t* keys, int8_t* values_t, int64_t batch,
+                        int64_t local_heads, int64_t head_dim, int64_t cap, const int* pos, float alpha_qk,
+                        float alpha_pv, int8_t* ctx, int64_t ld_ctx, cudaStream_t stream);
+int advance_position(int* pos, int by, cudaStream_t stream);
+
 }  // namespace ti

@@ -97,6 +97,9 @@ _c_tp_reduce_ln_q = _sig("ti_tp_reduce_layernorm_q",
                           [_ptr, _i32, _i64, _f32, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, ctypes.POINTER(_ptr), _i32,
                            _i64, _i64, _i64, _ptr])
 _c_tp_barrier = _sig("ti_tp_barrier", [ctypes.POINTER(_ptr), _i32, _i32, ctypes.c_uint32, _ptr])
+_c_decode_attention = _sig("ti_decode_attention_s8",
+                           [_ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _f32, _f32, _ptr, _i64, _ptr])
+_c_advance_position = _sig("ti_advance_position", [_ptr, _i32, _ptr])
 _c_transpose_values = _sig("ti_transpose_values", [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr])
 _c_last_error = _sig("ti_last_error", [], ctypes.c_char_p)
 _c_device_status = _sig("ti_device_status", [ctypes.POINTER(ctypes.c_int), _i32])
@@ -491,6 +494,39 @@ def tp_barrier(pad_ptrs, rank, epoch, device):
     arr = (_ptr * len(pad_ptrs))(*pad_ptrs)
     with _on_device(device):
         rc = _c_tp_barrier(arr, rank, len(pad_ptrs), epoch & 0xFFFFFFFF, _stream_ptr(device))
+    _check(rc)
+
+
+def decode_attention(qkv, keys, values_t, position, alpha_qk, alpha_pv):
+    """Attention of one new token per sequence over the int8 cache (ti_decode_attention_s8).
+    qkv int8 [B(+pad), 3*E] (q | k | v of the token); keys [B, cap, E]; values_t [B, Hl, D, cap];
+    position: int32 device tensor with the number of cached tokens.  Appends k and v to the cache
+    and returns the int8 context [B, E]."""
+    _require(keys, "keys", torch.int8, 3)
+    _require(values_t, "values_t", torch.int8, 4)
+    if not (isinstance(qkv, torch.Tensor) and qkv.is_cuda and qkv.dtype == torch.int8 and qkv.dim() == 2
+            and qkv.stride(1) == 1):
+        raise RuntimeError("qkv must be a 2-dimensional CUDA int8 tensor with contiguous rows")
+    if not (isinstance(position, torch.Tensor) and position.is_cuda and position.dtype == torch.int32
+            and position.numel() == 1):
+        raise RuntimeError("position must be a CUDA int32 tensor with one element")
+    b, hl, d, cap = values_t.shape
+    e = hl * d
+    if keys.shape != (b, cap, e) or qkv.shape[0] < b or qkv.shape[1] < 3 * e:
+        raise RuntimeError(f"keys {tuple(keys.shape)}, values_t {tuple(values_t.shape)} and qkv {tuple(qkv.shape)} disagree")
+    ctx = torch.empty((b, e), dtype=torch.int8, device=qkv.device)
+    with _on_device(qkv.device):
+        rc = _c_decode_attention(qkv.data_ptr(), qkv.stride(0), keys.data_ptr(), values_t.data_ptr(), b, hl, d, cap,
+                                 position.data_ptr(), float(alpha_qk), float(alpha_pv), ctx.data_ptr(), e,
+                                 _stream_ptr(qkv.device))
+    _check(rc)
+    return ctx
+
+
+def advance_position(position, by=1):
+    """position += by on the current stream (ti_advance_position)."""
+    with _on_device(position.device):
+        rc = _c_advance_position(position.data_ptr(), int(by), _stream_ptr(position.device))
     _check(rc)
 
 

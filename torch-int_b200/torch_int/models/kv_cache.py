@@ -20,6 +20,10 @@ class StaticInt8KVCache:
         self.local_heads = local_heads
         self.head_dim = head_dim
         self.length = 0  # positions filled so far (same for every layer once a forward ends)
+        # the same count in device memory: the one-token attention kernel reads it there, so a decode
+        # step has no per-step host parameters and can be replayed from a CUDA graph
+        self.pos = torch.zeros(1, dtype=torch.int32, device=device)
+        self.graph = None  # (CUDAGraph, static token buffer, static next-token buffer) of generate_greedy
         el = local_heads * head_dim
         self.keys = [torch.zeros((batch_size, self.capacity, el), dtype=torch.int8, device=device)
                      for _ in range(num_layers)]
@@ -28,6 +32,11 @@ class StaticInt8KVCache:
 
     def reset(self):
         self.length = 0
+        self.pos.zero_()
+
+    def set_length(self, n):
+        self.length = int(n)
+        self.pos.fill_(int(n))
 
     def store(self, layer_idx, k_view, v_view, bsz, tgt_len, past_len, b0=0):
         """Stores new keys and values at positions [past_len, past_len + T) of the sequences

@@ -171,7 +171,7 @@ class Int8OPTAttention(nn.Module):
     @torch.no_grad()
     def forward_fused(self, hidden_int8, cache: Optional[StaticInt8KVCache], layer_idx: int, past_len: int,
                       mask: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, b0: int = 0,
-                      context_only: bool = False):
+                      context_only: bool = False, decode: bool = False):
         """int8 [B,T,E] -> int32 partial sums of out_proj [B*T, E] (this rank's input
         slice; bias and scale are applied after the reduction over the ranks).  `out`:
         optional destination; `b0`: index of the first of these sequences in the cache."""
@@ -179,7 +179,7 @@ class Int8OPTAttention(nn.Module):
         hl, d, el = self.local_heads, self.head_dim, self.local_dim
         x2d = hidden_int8.view(-1, self.embed_dim)
         tokens = x2d.shape[0]
-        src_len = past_len + tgt_len
+        src_len = (past_len or 0) + tgt_len
         src_pad = _round_up(src_len, 16)
         # q, k and v in ONE GEMM over the concatenated weights (per-column alpha / beta); 16 spare
         # rows at the end keep the padded key reads of the last sequence inside the allocation
@@ -188,6 +188,17 @@ class Int8OPTAttention(nn.Module):
         C.gemm_i8_ex(x2d, w, qkv, bias, epilogue=C.EPI_S8_BIAS_S8_VEC, m=tokens, n=3 * el, k=self.embed_dim,
                      lda=self.embed_dim, ldb=self.embed_dim, ldc=3 * el, alpha_vec=alpha_vec, beta_vec=beta_vec)
         ld = 3 * el
+        if decode:
+            # one new token per sequence: append + scores + softmax + context in one kernel that reads
+            # the position from device memory (no per-step host parameters: CUDA-graph friendly)
+            ctx = C.decode_attention(qkv, cache.keys[layer_idx][b0:b0 + bsz], cache.values_t[layer_idx][b0:b0 + bsz],
+                                     cache.pos, self.qk_bmm._alpha(), self.pv_bmm._alpha()).view(bsz, 1, el)
+            if context_only:
+                return ctx
+            acc = out if out is not None else torch.empty((bsz, self.embed_dim), dtype=torch.int32, device=ctx.device)
+            C.gemm_i8_ex(ctx.view(bsz, el), self.out_proj.weight, acc, epilogue=C.EPI_S32_RAW, m=bsz,
+                         n=self.embed_dim, k=el, lda=el, ldb=el, ldc=self.embed_dim)
+            return acc
         q = qkv[:tokens, :el]
         k3 = qkv[:tokens].view(bsz, tgt_len, ld)[:, :, el:2 * el]
         v3 = qkv[:tokens].view(bsz, tgt_len, ld)[:, :, 2 * el:]
@@ -316,13 +327,14 @@ class Int8OPTDecoderLayer(nn.Module):
 
     # ------------------------------------------------------------------ fast path
     @torch.no_grad()
-    def forward_fused(self, residual, hidden_int8, cache, layer_idx, past_len, mask, next_ln: Optional[LayerNormQ]):
+    def forward_fused(self, residual, hidden_int8, cache, layer_idx, past_len, mask, next_ln: Optional[LayerNormQ],
+                      decode: bool = False):
         """residual fp [B,T,E], hidden_int8 = LayerNormQ(residual) -> (new residual,
         int8 input of the next layer or None).  `next_ln` is the next layer's
         self_attn_layer_norm (None after the last layer)."""
         shape = residual.shape
         attn = self.self_attn
-        acc = attn.forward_fused(hidden_int8, cache, layer_idx, past_len, mask)
+        acc = attn.forward_fused(hidden_int8, cache, layer_idx, past_len, mask, decode=decode)
         acc = self.tp.all_reduce_int32(acc)
         ln = self.final_layer_norm
         residual, h8 = C.dq_add_layernorm_q_bias(acc.view(shape), attn.out_proj._scalar("a"), attn.out_proj.bias,
@@ -555,6 +567,34 @@ class Int8OPTDecoder(nn.Module):
         return out
 
     @torch.no_grad()
+    def decode_step(self, tokens: torch.LongTensor, cache: StaticInt8KVCache) -> torch.Tensor:
+        """One new token per sequence ([B,1]) on top of `cache` (no padding tokens in the batch).
+        Everything position dependent reads cache.pos on the device, so the whole step is a fixed
+        sequence of launches with fixed arguments: it can be captured once in a CUDA graph and
+        replayed.  Returns the last hidden state [B,1,proj]."""
+        bsz = tokens.shape[0]
+        hidden = self.embed_tokens(tokens)
+        if self.project_in is not None:
+            hidden = self.project_in(hidden)
+        pos_ids = (cache.pos.long() + self.embed_positions.offset).view(1, 1).expand(bsz, 1)
+        hidden = hidden + nn.functional.embedding(pos_ids, self.embed_positions.weight)
+        residual = hidden.to(torch.float32).contiguous()
+        first = self.layers[0].self_attn_layer_norm
+        h8 = C.layernorm_q(residual, first.weight, first.bias, first.eps)
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            next_ln = self.layers[i + 1].self_attn_layer_norm if i + 1 < n else None
+            residual, h8 = layer.forward_fused(residual, h8, cache, i, None, None, next_ln, decode=True)
+        C.advance_position(cache.pos, 1)
+        cache.length += 1
+        residual = residual.to(hidden.dtype)
+        if self.final_layer_norm is not None:
+            residual = self.final_layer_norm(residual)
+        if self.project_out is not None:
+            residual = self.project_out(residual)
+        return residual
+
+    @torch.no_grad()
     def forward(self, input_ids: torch.LongTensor, attention_mask: Optional[torch.Tensor] = None,
                 past_key_values: Optional[StaticInt8KVCache] = None, use_cache: bool = False,
                 reference_path: bool = False) -> DecoderOutput:
@@ -604,7 +644,7 @@ class Int8OPTDecoder(nn.Module):
                     next_ln = self.layers[i + 1].self_attn_layer_norm if i + 1 < n else None
                     residual, h8 = layer.forward_fused(residual, h8, cache, i, past_len, mask, next_ln)
             if cache is not None:
-                cache.length = src_len
+                cache.set_length(src_len)
             residual = residual.to(hidden.dtype)
         if self.final_layer_norm is not None:
             residual = self.final_layer_norm(residual)
@@ -694,19 +734,53 @@ class Int8OPTForCausalLM(nn.Module):
         return CausalLMOutput(logits, out.past_key_values)
 
     @torch.no_grad()
-    def generate_greedy(self, input_ids, max_new_tokens: int, cache: Optional[StaticInt8KVCache] = None):
-        """Prefill + greedy decoding with the static int8 cache.  Returns [B, T + new]."""
+    def decode_step(self, tokens, cache: StaticInt8KVCache):
+        """Logits [B, vocab] of the token after `tokens` [B,1], appended to `cache`."""
+        hidden = self.model.decoder.decode_step(tokens, cache)
+        return self.lm_head(hidden[:, -1, :].to(self.lm_head.weight.dtype))
+
+    @torch.no_grad()
+    def generate_greedy(self, input_ids, max_new_tokens: int, cache: Optional[StaticInt8KVCache] = None,
+                        use_cuda_graph: Optional[bool] = None):
+        """Prefill + greedy decoding with the static int8 cache.  Returns [B, T + new].
+        With use_cuda_graph (default on a single GPU) the decode step is captured once per cache -
+        after a first eager step has initialised everything lazy - and replayed for the other steps."""
         bsz, t = input_ids.shape
         if cache is None:
             cache = self.new_cache(bsz, t + max_new_tokens)
         else:
-            cache.length = 0
+            cache.reset()
+        if t + max_new_tokens > cache.capacity:
+            raise RuntimeError(f"cache capacity {cache.capacity} is too small for {t} + {max_new_tokens} tokens")
+        if use_cuda_graph is None:
+            use_cuda_graph = self.model.decoder.tp.size == 1
         out = self.forward(input_ids, past_key_values=cache, use_cache=True, last_token_only=True)
         tokens = [input_ids]
         nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
-        for _ in range(max_new_tokens - 1):
+        steps_left = max_new_tokens - 1
+        if steps_left > 0:  # first decode step eagerly (also warms up everything a capture must not do)
             tokens.append(nxt)
-            out = self.forward(nxt, past_key_values=cache, use_cache=True, last_token_only=True)
-            nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+            nxt = self.decode_step(nxt, cache).argmax(dim=-1, keepdim=True)
+            steps_left -= 1
+        if use_cuda_graph and steps_left > 0:
+            if cache.graph is None or cache.graph[1].shape != nxt.shape:
+                static_tok = nxt.clone()
+                length = cache.length
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    static_next = self.decode_step(static_tok, cache).argmax(dim=-1, keepdim=True)
+                cache.length = length  # capturing records the step, it does not run it
+                cache.graph = (graph, static_tok, static_next)
+            graph, static_tok, static_next = cache.graph
+            for _ in range(steps_left):
+                tokens.append(nxt)
+                static_tok.copy_(nxt)
+                graph.replay()
+                cache.length += 1
+                nxt = static_next.clone()
+        else:
+            for _ in range(steps_left):
+                tokens.append(nxt)
+                nxt = self.decode_step(nxt, cache).argmax(dim=-1, keepdim=True)
         tokens.append(nxt)
         return torch.cat(tokens, dim=1)
