@@ -338,6 +338,177 @@ def opt_cpu_sample(arch, batch, seq, tokens=64):
                         f"extrapolated x{layers} layers (embeddings and lm_head not included)"), O.num_threads()
 
 
+# ------------------------------------------------------------- op-level workloads (HBM bound)
+def _event_time(fn, reps):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+class RowKernelWorkload:
+    """LayerNormQ, dq_add_layernorm_q and softmax_q at the shapes of the OPT-13B layer config
+    ([4,512,5120]) and of the OPT-175B config ([16,1024,12288]); several buffers are rotated so that
+    no launch finds its input in L2.  value = GB/s of the dq_add_layernorm_q kernel at the large shape."""
+    name = "row_kernels_layernormq_dq_add_ln_q_softmax_q"
+    metric = "dq_add_layernorm_q_gbytes_per_s"
+    unit = "GB/s"
+    dtype = "fp32 residual / int32 accumulators in, int8 out"
+    scaling = "weak"
+    launches_per_step = 1
+
+    def __init__(self, device):
+        from torch_int import _CUDA as C
+        self.C, self.device = C, device
+        self.h2d = self.d2h = 0
+        self.cases = {}
+        rot = 3
+        rows, h = 16 * 1024, 12288
+        self.acc = [torch.randint(-200000, 200000, (rows, h), dtype=torch.int32, device=device) for _ in range(rot)]
+        self.res = [torch.randn((rows, h), device=device) for _ in range(rot)]
+        self.gamma = torch.rand(h, device=device) * 20 + 10
+        self.beta = torch.randn(h, device=device)
+        self.i = 0
+        self.bytes_per_step = rows * h * 13.0
+
+    def step(self):
+        self.i = (self.i + 1) % len(self.acc)
+        return self.C.dq_add_layernorm_q(self.acc[self.i], 1e-5, self.res[self.i], self.gamma, self.beta, 1e-5)
+
+    step_e2e = step
+
+    def units(self, n_gpus):
+        return self.bytes_per_step * n_gpus / 1e9
+
+    def measure_cases(self, peaks):
+        C, dev = self.C, self.device
+        out = {}
+        for label, (rows, h) in {"4x512x5120": (2048, 5120), "16x1024x12288": (16384, 12288)}.items():
+            rot = 4 if rows * h < 5e7 else 3
+            xs = [torch.randn((rows, h), device=dev) for _ in range(rot)]
+            accs = [torch.randint(-200000, 200000, (rows, h), dtype=torch.int32, device=dev) for _ in range(rot)]
+            g, b = torch.rand(h, device=dev) * 20 + 10, torch.randn(h, device=dev)
+            k = [0]
+
+            def ln():
+                k[0] = (k[0] + 1) % rot
+                C.layernorm_q(xs[k[0]], g, b, 1e-5)
+
+            def dq():
+                k[0] = (k[0] + 1) % rot
+                C.dq_add_layernorm_q(accs[k[0]], 1e-5, xs[k[0]], g, b, 1e-5)
+            for name, fn, bpe in (("layernorm_q", ln, 5.0), ("dq_add_layernorm_q", dq, 13.0)):
+                ms = _event_time(fn, 50)
+                gbs = rows * h * bpe / (ms * 1e-3) / 1e9
+                out[f"{name} {label}"] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+            del xs, accs
+        for label, (bh, t, s) in {"4x40 heads, S=512": (160, 512, 512), "4x40 heads, S=2048": (160, 2048, 2048)}.items():
+            sc = [torch.randn((bh, t, s), device=dev) * 2 for _ in range(2)]
+            k = [0]
+
+            def sm():
+                k[0] ^= 1
+                C.softmax_q(sc[k[0]], None, 40, causal=0)
+            ms = _event_time(sm, 20)
+            # causal: on average half of each row is read; all of it is written
+            gbs = bh * t * s * (4.0 * 0.5 + 1.0) / (ms * 1e-3) / 1e9
+            out[f"softmax_q causal {label}"] = {"ms": round(ms, 4), "GB/s (algorithmic: half read + all written)": round(gbs, 1),
+                                                "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+            del sc
+        return out
+
+    def config(self, n_gpus):
+        return {"workload": self.name, "rows": 16384, "H": 12288, "bytes_per_element": 13,
+                "l2": "three rotating input sets of 1.6 GB each: no launch finds its input in L2"}
+
+    def roofline(self, ms, peaks):
+        gbs = self.bytes_per_step / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None,
+                "kernel": "dq_add_layernorm_q_kernel<float, 256, 12> at [16384, 12288] (13 B/element)",
+                "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
+                "cases": self.measure_cases(peaks)}
+
+    def cpu_sample(self):
+        from oracle import w8a8 as O
+        rows, h = 512, 12288
+        acc = torch.randint(-200000, 200000, (rows, h), dtype=torch.int32)
+        res, g, b = torch.randn(rows, h), torch.rand(h) * 20 + 10, torch.randn(h)
+
+        def run():
+            return O.dq_add_layernorm_q(acc, 1e-5, res, g, b, 1e-5)
+        return run, rows * h * 13.0 / 1e9, f"{rows} of 16384 rows (the reference's dq_add_layernorm_q_py on CPU)", torch.get_num_threads()
+
+
+class BmmWorkload:
+    """The attention products at batch*heads = 4*40, head_dim 128, seq 128/512/2048: Q.K^T -> fp32 and
+    P.V -> int8.  value = GB/s (algorithmic bytes) of Q.K^T at S = 2048, which is HBM-write bound."""
+    name = "attention_bmm_sweep_bh160_d128"
+    metric = "bmm_s8t_s8n_f32t_gbytes_per_s"
+    unit = "GB/s"
+    dtype = "int8 x int8 -> int32, fp32 / int8 out"
+    scaling = "weak"
+    launches_per_step = 1
+
+    def __init__(self, device):
+        from torch_int import _CUDA as C
+        self.C, self.device = C, device
+        self.h2d = self.d2h = 0
+        bh, s, d = 160, 2048, 128
+        self.q = torch.randint(-127, 128, (bh, s, d), dtype=torch.int8, device=device)
+        self.k = torch.randint(-127, 128, (bh, s, d), dtype=torch.int8, device=device)
+        self.bytes_per_step = bh * (2 * s * d + 4.0 * s * s)
+
+    def step(self):
+        return self.C.bmm_s8t_s8n_f32t(self.q, self.k, 1.0 / 127 ** 2)
+
+    step_e2e = step
+
+    def units(self, n_gpus):
+        return self.bytes_per_step * n_gpus / 1e9
+
+    def config(self, n_gpus):
+        return {"workload": self.name, "batch_heads": 160, "head_dim": 128, "seq": 2048,
+                "l2": "the 2.7 GB fp32 output exceeds L2"}
+
+    def roofline(self, ms, peaks):
+        C, dev = self.C, self.device
+        cases = {}
+        bh, d = 160, 128
+        for s in (128, 512, 2048):
+            q = torch.randint(-127, 128, (bh, s, d), dtype=torch.int8, device=dev)
+            k = torch.randint(-127, 128, (bh, s, d), dtype=torch.int8, device=dev)
+            p = torch.randint(-127, 128, (bh, s, s), dtype=torch.int8, device=dev)
+            vt = torch.randint(-127, 128, (bh, d, s), dtype=torch.int8, device=dev)
+            t1 = _event_time(lambda: C.bmm_s8t_s8n_f32t(q, k, 1.0 / 127 ** 2), 20)
+            t2 = _event_time(lambda: C.bmm_s8t_s8n_s8t(p, vt, 0.01), 20)
+            b1, b2 = bh * (2 * s * d + 4.0 * s * s), bh * (s * s + 2.0 * s * d)
+            ops = 2.0 * bh * s * s * d
+            cases[f"S={s}"] = {"qk_f32t_ms": round(t1, 4), "qk_GB/s": round(b1 / t1 / 1e6, 1), "qk_TOP/s": round(ops / t1 / 1e9, 1),
+                               "pv_s8t_ms": round(t2, 4), "pv_GB/s": round(b2 / t2 / 1e6, 1), "pv_TOP/s": round(ops / t2 / 1e9, 1)}
+        gbs = self.bytes_per_step / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None,
+                "kernel": "gemm_i8_kernel<256, EPI_F32_ALPHA, PAIR> on [160, 2048, 128] x [160, 2048, 128]^T",
+                "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})", "cases": cases}
+
+    def cpu_sample(self):
+        from oracle import w8a8 as O
+        g = torch.Generator().manual_seed(0)
+        q = torch.randint(-127, 128, (4, 2048, 128), generator=g, dtype=torch.int8)
+        k = torch.randint(-127, 128, (4, 2048, 128), generator=g, dtype=torch.int8)
+
+        def run():
+            return O.bmm_s8t_s8n_f32t(q, k, 1.0 / 127 ** 2)
+        return run, 4 * (2 * 2048 * 128 + 4.0 * 2048 * 2048) / 1e9, "4 of the 160 (batch, head) products at S = 2048", O.num_threads()
+
+
 def time_steps(fn, steps, warmup, world):
     import torch.distributed as dist
     for _ in range(warmup):
@@ -380,7 +551,7 @@ def cpu_baseline(wl, min_seconds=10.0, max_reps=50):
 def pick_workload(name, world):
     if name in (None, "auto"):
         name = "opt30b" if world == 1 else "opt175b"
-    if name == "gemm" or name in OPT_WORKLOADS:
+    if name in ("gemm", "norm", "bmm") or name in OPT_WORKLOADS:
         return name
     raise SystemExit(f"unknown workload {name}")
 
@@ -405,6 +576,11 @@ def run_reference(args, world, rank):
         metric, unit, dtype, scaling, name = (GemmWorkload.metric, GemmWorkload.unit, GemmWorkload.dtype,
                                               GemmWorkload.scaling, GemmWorkload.name)
         config = {"workload": name, "M": HG[0], "N": HG[1], "K": HG[2], "sample": sample}
+    elif key in ("norm", "bmm"):
+        WL = RowKernelWorkload if key == "norm" else BmmWorkload
+        run, units, sample, cores = WL.cpu_sample(None)
+        metric, unit, dtype, scaling, name = WL.metric, WL.unit, WL.dtype, WL.scaling, WL.name
+        config = {"workload": name, "sample": sample}
     else:
         arch, batch, seq, _ = OPT_WORKLOADS[key]
         run, units, sample, cores = opt_cpu_sample(arch, batch, seq)
@@ -445,9 +621,9 @@ def main():
     world, rank, local = dist_env()
     key = pick_workload(args.workload, world)
     if args.steps is None:
-        args.steps = 1000 if key == "gemm" else 10
+        args.steps = {"gemm": 1000, "norm": 200, "bmm": 100}.get(key, 10)
     if args.warmup is None:
-        args.warmup = 5 if key == "gemm" else 3
+        args.warmup = 5 if key in ("gemm", "norm", "bmm") else 3
     if args.impl == "reference":
         run_reference(args, world, rank)
         return
@@ -459,7 +635,14 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    wl = GemmWorkload(device) if key == "gemm" else OptWorkload(device, key, world, rank)
+    if key == "gemm":
+        wl = GemmWorkload(device)
+    elif key == "norm":
+        wl = RowKernelWorkload(device)
+    elif key == "bmm":
+        wl = BmmWorkload(device)
+    else:
+        wl = OptWorkload(device, key, world, rank)
     peaks = measured_peaks()
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -469,7 +652,7 @@ def main():
     clocks = sampler.stop() if sampler else None
     ms_e2e = ms if args.profile else time_steps(wl.step_e2e, args.steps, args.warmup, world)
     extra = {}
-    if key != "gemm" and not args.profile and not args.no_decode:
+    if key in OPT_WORKLOADS and not args.profile and not args.no_decode:
         extra = wl.decode_rate()
     from torch_int import _CUDA as C
     status = C.device_status()
