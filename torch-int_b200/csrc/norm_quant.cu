@@ -384,6 +384,67 @@ softmax_q_warp_kernel(const float* __restrict__ scores, const float* __restrict_
   }
 }
 
+// Streaming form of the warp-per-row softmax for long rows (more than 32*4*8 floats): the row is
+// read three times - maximum, sum of exponentials, probabilities - instead of being kept in
+// registers; the second and third reads hit L1/L2 (a row is at most 64 KB), DRAM traffic stays
+// one read and one write, and the low register count keeps many warps resident.  Per-lane
+// accumulation order and all arithmetic are those of softmax_q_warp_kernel, so both forms give
+// identical results.
+__global__ void __launch_bounds__(256)
+softmax_q_warp_stream_kernel(const float* __restrict__ scores, const float* __restrict__ mask,
+                             int8_t* __restrict__ out, long long rows, int T, int S, int heads,
+                             long long lds, long long ldo, int causal) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int t = static_cast<int>(row % T);
+  const long long bh = row / T;
+  const float* sr = scores + row * lds;
+  const float* mr = mask ? mask + ((bh / heads) * T + t) * static_cast<long long>(S) : nullptr;
+  const int s4 = S >> 2;
+  const int lim = (mr == nullptr && causal >= 0) ? t + causal : 0x7fffffff;
+  const int n4 = min(s4, lim / 4 + 1);  // chunks that hold at least one visible column
+  auto load = [&](int i) -> float4 {
+    float4 a = *reinterpret_cast<const float4*>(sr + 4 * i);
+    if (mr) {
+      const float4 m = *reinterpret_cast<const float4*>(mr + 4 * i);
+      a.x += m.x; a.y += m.y; a.z += m.z; a.w += m.w;
+    } else {
+      if (4 * i + 1 > lim) a.y += -FLT_MAX;
+      if (4 * i + 2 > lim) a.z += -FLT_MAX;
+      if (4 * i + 3 > lim) a.w += -FLT_MAX;
+    }
+    a.x = fmaxf(a.x, -FLT_MAX); a.y = fmaxf(a.y, -FLT_MAX);
+    a.z = fmaxf(a.z, -FLT_MAX); a.w = fmaxf(a.w, -FLT_MAX);
+    return a;
+  };
+  float mx = -FLT_MAX;
+#pragma unroll 4
+  for (int i = lane; i < n4; i += 32) {
+    const float4 a = load(i);
+    mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll 4
+  for (int i = lane; i < n4; i += 32) {
+    const float4 a = load(i);
+    sum += (expf(a.x - mx) + expf(a.y - mx)) + (expf(a.z - mx) + expf(a.w - mx));
+  }
+  sum = warp_sum(sum);
+  int8_t* orow = out + row * ldo;
+#pragma unroll 4
+  for (int i = lane; i < s4; i += 32) {
+    uint32_t packed = 0;
+    if (i < n4) {
+      const float4 a = load(i);
+      packed = pack_s8x4(__fdiv_rn(expf(a.x - mx), sum) * 127.f, __fdiv_rn(expf(a.y - mx), sum) * 127.f,
+                         __fdiv_rn(expf(a.z - mx), sum) * 127.f, __fdiv_rn(expf(a.w - mx), sum) * 127.f);
+    }
+    *reinterpret_cast<uint32_t*>(orow + 4 * i) = packed;
+  }
+}
+
 // int8 [B, T, H, D] -> [B, H, D, ld_out] at column offset col0 (the transposed,
 // K-major value layout P.V needs).  64 x 64 byte tiles through shared memory,
 // 4-byte accesses on both sides.
@@ -708,7 +769,12 @@ int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch
     else if (wv <= 2) TI_SOFTMAX_WARP(2);
     else if (wv <= 4) TI_SOFTMAX_WARP(4);
     else if (wv <= 8) TI_SOFTMAX_WARP(8);
-    else TI_SOFTMAX_WARP(16);
+    else
+      rc = check_launch("softmax_q_warp_stream", [&] {
+        softmax_q_warp_stream_kernel<<<wgrid, 256, 0, stream>>>(scores, mask, out, rows, static_cast<int>(T),
+                                                                static_cast<int>(S), static_cast<int>(heads),
+                                                                lds, ldo, causal);
+      });
 #undef TI_SOFTMAX_WARP
     return rc;
   }
