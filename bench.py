@@ -98,6 +98,22 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def start_watchdog(seconds, rank):
+    """Ends the process if the benchmark has not finished after `seconds` (a hung collective or a
+    machine problem must not hold the GPUs until an outer limit kills the job)."""
+    def fire():
+        msg = f"bench.py watchdog: not finished after {seconds} s, giving up"
+        sys.stderr.write(msg + "\n")
+        sys.stderr.flush()
+        if rank == 0:
+            print(json.dumps({"error": msg}), flush=True)
+        os._exit(3)
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+    return t
+
+
 def dist_env():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -630,11 +646,13 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    start_watchdog(int(os.environ.get("TI_BENCH_DEADLINE_S", "900")), rank)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
+        import datetime
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     if key == "gemm":
         wl = GemmWorkload(device)
     elif key == "norm":
@@ -644,6 +662,24 @@ def main():
     else:
         wl = OptWorkload(device, key, world, rank)
     peaks = measured_peaks()
+    from torch_int import _CUDA as C
+
+    def agreed_status():
+        """Kernel status word, maximum over the ranks (every rank takes the same decision)."""
+        st = C.device_status(reset=True)
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([st], dtype=torch.int32, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            st = int(t.item())
+        return st
+
+    if key in OPT_WORKLOADS and world > 1 and agreed_status() != 0 and wl.tp.use_peer_memory:
+        # the first step (run while the workload was built) hit a bounded-wait time limit in the
+        # peer-memory exchange: use NCCL collectives for the measurement instead
+        wl.tp.use_peer_memory = False
+        wl.step()
+        assert agreed_status() == 0, "a kernel reported a wait timeout"
 
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
@@ -654,8 +690,7 @@ def main():
     extra = {}
     if key in OPT_WORKLOADS and not args.profile and not args.no_decode:
         extra = wl.decode_rate()
-    from torch_int import _CUDA as C
-    status = C.device_status()
+    status = agreed_status()
     assert status == 0, f"a kernel reported wait timeout {status}"
     if rank == 0:
         units = wl.units(world)

@@ -2,7 +2,8 @@
 
 Run in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]      (default /root/reference)
+    python tests/golden/make_golden.py /path/to/reference-checkout
+(or set TORCH_INT_REFERENCE to that path)
 
 What comes from where:
   * layernorm_q.npz, dq_add_layernorm_q.npz, quantize_absmax.npz: outputs of the
@@ -31,7 +32,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TORCH_INT_REFERENCE", "")
+if not REF or not os.path.isdir(os.path.join(REF, "torch_int")):
+    raise SystemExit("usage: make_golden.py /path/to/reference-checkout (a directory holding torch_int/)")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -583,6 +583,10 @@ __global__ void tp_barrier_kernel(PeerPtrs pads, int rank, int n, uint32_t epoch
     __threadfence_system();
     uint32_t* theirs = static_cast<uint32_t*>(pads.p[t]) + rank;
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+    // Once any wait of this process has given up, later barriers still signal (so healthy peers are
+    // not held up by us) but no longer wait: a broken exchange then costs one time limit in total,
+    // not one per barrier, and the host finds the error in the status word afterwards.
+    if (*reinterpret_cast<volatile int*>(status) != 0) return;
     const uint32_t* mine = static_cast<const uint32_t*>(pads.p[rank]) + t;
     unsigned long long t0 = 0;
     for (unsigned it = 0;; ++it) {

@@ -182,6 +182,15 @@ class PeerWorkspace:
         dist.barrier(group=group)  # every rank's pads are zero before the first barrier kernel
         self.epoch = 0
         self.pad_ptrs = [p + self.pad_off for p in self.ptrs]
+        # Preflight: a few barriers over the fresh pads.  If peer stores or loads do not work on this
+        # machine the (bounded) waits give up and set the status word; every rank then learns of it
+        # through one NCCL reduction and the caller falls back to NCCL collectives.
+        for _ in range(3):
+            self.barrier()
+        flag = torch.tensor([C.device_status(reset=True)], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+        if int(flag.item()) != 0:
+            raise RuntimeError(f"peer-memory barrier preflight failed (status {int(flag.item())})")
         # every rank's stage as a tensor of this process (peer mappings), for contiguous peer copies
         self.peer_stage = [self.handle.get_buffer(o, (chunks, n, ms, e), torch.int32, 0) for o in range(n)]
 
