@@ -126,7 +126,8 @@ class GemmWorkload:
     name = "w8a8_gemm_4096x12288x12288_int8out"
     metric = "w8a8_gemm_tops"
     unit = "TOP/s"
-    dtype = "int8 x int8 -> int32, fp32 epilogue, int8 out"
+    dtype = "int8"
+    arithmetic = "int8 x int8 -> int32 on tcgen05 (kind::i8), fp32 epilogue, int8 out"
     scaling = "weak"
 
     def __init__(self, device):
@@ -159,7 +160,7 @@ class GemmWorkload:
 
     def config(self, n_gpus):
         return {"workload": self.name, "M": HG[0], "N": HG[1], "K": HG[2], "alpha": self.alpha,
-                "beta": self.beta, "replicas": n_gpus,
+                "beta": self.beta, "replicas": n_gpus, "arithmetic": self.arithmetic,
                 "l2": "inputs (201 MB of int8 operands) exceed the 126 MB L2"}
 
     def roofline(self, ms, peaks):
@@ -198,7 +199,8 @@ OPT_WORKLOADS = {
 class OptWorkload:
     metric = "int8_opt_prefill_tokens_per_s"
     unit = "tokens/s"
-    dtype = "int8 x int8 -> int32 GEMM/BMM, fp32 epilogues and residual stream, fp16 embeddings and lm_head"
+    dtype = "int8"
+    arithmetic = "int8 x int8 -> int32 GEMM/BMM, fp32 epilogues and residual stream, fp16 embeddings and lm_head"
     scaling = "strong"
 
     def __init__(self, device, key, world, rank):
@@ -248,6 +250,7 @@ class OptWorkload:
         return {"workload": self.name, "architecture": self.arch, "layers": self.cfg.num_hidden_layers,
                 "hidden": self.cfg.hidden_size, "heads": self.cfg.num_attention_heads, "ffn": self.cfg.ffn_dim,
                 "vocab": self.cfg.vocab_size, "batch": self.batch, "prefill_len": self.seq,
+                "arithmetic": self.arithmetic,
                 "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single GPU",
                 "exchange": ("none" if n_gpus == 1 else
                              (f"peer memory ({self.tp.peer_mode}): partial sums to the owners' slabs -> barrier -> "
@@ -375,7 +378,7 @@ class RowKernelWorkload:
     name = "row_kernels_layernormq_dq_add_ln_q_softmax_q"
     metric = "dq_add_layernorm_q_gbytes_per_s"
     unit = "GB/s"
-    dtype = "fp32 residual / int32 accumulators in, int8 out"
+    dtype = "f32"
     scaling = "weak"
     launches_per_step = 1
 
@@ -468,7 +471,7 @@ class BmmWorkload:
     name = "attention_bmm_sweep_bh160_d128"
     metric = "bmm_s8t_s8n_f32t_gbytes_per_s"
     unit = "GB/s"
-    dtype = "int8 x int8 -> int32, fp32 / int8 out"
+    dtype = "int8"
     scaling = "weak"
     launches_per_step = 1
 
@@ -646,7 +649,7 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
-    start_watchdog(int(os.environ.get("TI_BENCH_DEADLINE_S", "900")), rank)
+    start_watchdog(int(os.environ.get("TI_BENCH_DEADLINE_S", "600")), rank)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
