@@ -71,6 +71,25 @@ def test_dq_add_layernorm_q_vs_oracle(cuda_ops, shape):
     assert_quant_close(q, q_o, 0.999, str(shape) + " with bias")
 
 
+def test_dq_add_layernorm_q_vs_reference_cpp(cuda_ops):
+    """The GPU kernel against the reference's own C++ op (torch_int/kernels/fused.cu) compiled into
+    oracle/_ref and run on CPU tensors; skipped where that module has not been built."""
+    from oracle import build_ref
+    ref = build_ref.load()
+    if ref is None:
+        pytest.skip("oracle/_ref/ref_fused.so is not built")
+    for shape, scale in (((2, 3, 4), 0.01), ((4, 128, 5120), 1.3e-5), ((1, 64, 12288), 2e-5)):
+        h = shape[-1]
+        g = torch.Generator().manual_seed(h)
+        x = torch.randint(-200000, 200000, shape, generator=g, dtype=torch.int32)
+        res = randn(shape, 11)
+        gamma, beta = affine(h, 12, 30.0)
+        r_ref, q_ref = ref.dq_add_layernorm_q(x, scale, res, gamma, beta, 1e-5)
+        r, q = cuda_ops.dq_add_layernorm_q(x.cuda(), scale, res.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+        assert torch.equal(r.cpu(), r_ref), f"residual output {shape}"
+        assert_quant_close(q, q_ref, 0.999, f"q {shape}")
+
+
 def test_dq_add_module(cuda_ops):
     from torch_int.nn.fused import DQ_Add_LayerNorm_Q
     m = DQ_Add_LayerNorm_Q(256).cuda()
