@@ -101,3 +101,21 @@ def test_causal_lm_from_float():
     assert got.shape == want.shape
     assert _r2(got, want) < 0.05, _r2(got, want)
     assert float((got.argmax(-1) == want.argmax(-1)).double().mean()) > 0.8
+
+
+def test_from_float_model_saves_and_loads(tmp_path):
+    """A quantised model as from_float leaves it (transformers' config object, the float embedding modules
+    of the source model) goes through save_pretrained / from_pretrained unchanged."""
+    from torch_int.models.opt import Int8OPTForCausalLM
+    torch.manual_seed(4)
+    cfg = _config(layers=1)
+    model = OPTForCausalLM(cfg).eval()
+    scales = [dict(attn_input_scale=0.05, q_output_scale=0.04, k_output_scale=0.04, v_output_scale=0.03,
+                   out_input_scale=0.02, fc1_input_scale=0.05, fc2_input_scale=0.03)]
+    int8_model = Int8OPTForCausalLM.from_float(model, scales)
+    int8_model.save_pretrained(str(tmp_path))
+    again = Int8OPTForCausalLM.from_pretrained(str(tmp_path), device="cpu")
+    a, b = int8_model.state_dict(), again.state_dict()
+    assert set(a) == set(b)
+    for k in a:
+        assert torch.equal(a[k].reshape(-1).float(), b[k].reshape(-1).float()), k

@@ -680,6 +680,20 @@ class Int8OPTModel(nn.Module):
         int8_module.decoder = Int8OPTDecoder.from_float(module.decoder, decoder_layer_scales)
         return int8_module
 
+    @classmethod
+    def from_pretrained(cls, directory, device="cuda", torch_dtype=None, tp: Optional[TensorParallel] = None,
+                        strict: bool = True, device_map=None):
+        """Loads a checkpoint directory in the transformers layout (config.json + state-dict files with
+        the reference's buffer names), as the reference's inherited ``from_pretrained`` does
+        (benchmark/bench_opt.py:35-40).  With `tp`, each rank reads only its slices of the split weights."""
+        from .checkpoint import load_pretrained
+        return load_pretrained(cls, directory, device=device, torch_dtype=torch_dtype, tp=tp, strict=strict,
+                               device_map=device_map)
+
+    def save_pretrained(self, directory, max_shard_bytes: int = 5 << 30, safe_serialization: bool = True):
+        from .checkpoint import save_pretrained
+        return save_pretrained(self, directory, max_shard_bytes, safe_serialization)
+
 
 class Int8OPTForCausalLM(nn.Module):
     """Int8 OPT with the language-model head, which is tied to the token embeddings
@@ -700,6 +714,20 @@ class Int8OPTForCausalLM(nn.Module):
         int8_module.model = Int8OPTModel.from_float(module.model, decoder_layer_scales)
         int8_module.lm_head = module.lm_head
         return int8_module
+
+    @classmethod
+    def from_pretrained(cls, directory, device="cuda", torch_dtype=None, tp: Optional[TensorParallel] = None,
+                        strict: bool = True, device_map=None):
+        """Loads a checkpoint directory in the transformers layout (config.json + state-dict files with
+        the reference's buffer names), as the reference's inherited ``from_pretrained`` does
+        (benchmark/bench_opt.py:35-40).  With `tp`, each rank reads only its slices of the split weights."""
+        from .checkpoint import load_pretrained
+        return load_pretrained(cls, directory, device=device, torch_dtype=torch_dtype, tp=tp, strict=strict,
+                               device_map=device_map)
+
+    def save_pretrained(self, directory, max_shard_bytes: int = 5 << 30, safe_serialization: bool = True):
+        from .checkpoint import save_pretrained
+        return save_pretrained(self, directory, max_shard_bytes, safe_serialization)
 
     def get_input_embeddings(self):
         return self.model.decoder.embed_tokens

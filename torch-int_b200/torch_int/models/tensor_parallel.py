@@ -18,7 +18,7 @@ import torch.distributed as dist
 
 
 class TensorParallel:
-    def __init__(self, size: int = 1, rank: int = 0, group=None, max_chunks: int = 8,
+    def __init__(self, size: int = 1, rank: int = 0, group=None, max_chunks: int = 4,
                  min_pipeline_tokens: int = 1024):
         self.size = size
         self.rank = rank
@@ -121,23 +121,40 @@ class TensorParallel:
         s = n // self.size
         return t[..., self.rank * s:(self.rank + 1) * s].contiguous()
 
+    @staticmethod
+    def shard_dim(name: str):
+        """Which dimension of the Int8 OPT buffer `name` is split over the ranks (None = replicated).
+        Column-parallel linears (q/k/v/fc1): rows of `weight` (0) and entries of `bias` (-1).
+        Row-parallel linears (out_proj/fc2): columns of `weight` (1); their fp32 bias is kept whole
+        on every rank, since it is applied after the reduction.  Scales, LayerNorm parameters and
+        embeddings are replicated."""
+        parts = name.split(".")
+        leaf, owner = parts[-1], parts[-2] if len(parts) > 1 else ""
+        if owner in ("q_proj", "k_proj", "v_proj", "fc1"):
+            return 0 if leaf == "weight" else -1 if leaf == "bias" else None
+        if owner in ("out_proj", "fc2") and leaf == "weight":
+            return 1
+        return None
+
+    def shard_range(self, n: int):
+        """[start, stop) of this rank's part of an extent-n split dimension."""
+        if n % self.size != 0:
+            raise ValueError(f"extent {n} cannot be split over {self.size} ranks")
+        s = n // self.size
+        return self.rank * s, (self.rank + 1) * s
+
     def shard_state_dict(self, full: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        """This rank's slice of a single-GPU Int8 OPT state dict.  Column-parallel
-        linears (q/k/v/fc1): rows of `weight`, entries of the [1,N] `bias`.
-        Row-parallel linears (out_proj/fc2): columns of `weight`; the fp32 bias is
-        kept whole on every rank (it is applied after the reduction).  Everything
-        else (scales, LayerNorm parameters, embeddings) is replicated."""
+        """This rank's slice (see shard_dim) of a single-GPU Int8 OPT state dict."""
         if self.size == 1:
             return dict(full)
         out = {}
         for name, t in full.items():
-            parts = name.split(".")
-            leaf, owner = parts[-1], parts[-2] if len(parts) > 1 else ""
-            if owner in ("q_proj", "k_proj", "v_proj", "fc1") and leaf == "weight":
+            dim = self.shard_dim(name)
+            if dim == 0:
                 out[name] = self._rows(t)
-            elif owner in ("q_proj", "k_proj", "v_proj", "fc1") and leaf == "bias":
+            elif dim == -1:
                 out[name] = self._cols(t.reshape(1, -1))
-            elif owner in ("out_proj", "fc2") and leaf == "weight":
+            elif dim == 1:
                 out[name] = self._cols(t)
             else:
                 out[name] = t
