@@ -634,6 +634,10 @@ def main():
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-rate measurement of the OPT workloads")
+    ap.add_argument("--trace", default=None, metavar="DIR",
+                    help="tensor-parallel OPT workloads: after the measurement run one more step with CUDA events "
+                         "around every compute phase and exchange stage, write DIR/tp_trace_rank<r>.json (Chrome "
+                         "trace format) and add the per-stream busy times to the JSON line")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for ncu: no end-to-end leg, no CPU baseline")
     args = ap.parse_args()
@@ -693,6 +697,18 @@ def main():
     extra = {}
     if key in OPT_WORKLOADS and not args.profile and not args.no_decode:
         extra = wl.decode_rate()
+    if args.trace and key in OPT_WORKLOADS and world > 1:
+        from torch_int.models.tensor_parallel import StreamTrace
+        wl.tp.trace = StreamTrace()
+        wl.step()
+        torch.cuda.synchronize()
+        trace, wl.tp.trace = wl.tp.trace, None
+        os.makedirs(args.trace, exist_ok=True)
+        trace.dump(os.path.join(args.trace, f"tp_trace_rank{rank}.json"), pid=rank)
+        extra["tp_trace"] = {row: {"busy_ms": round(v["busy_us"] / 1e3, 2),
+                                   "extent_ms": round((v["last_us"] - v["first_us"]) / 1e3, 2),
+                                   "by_name_ms": {k: round(t / 1e3, 2) for k, t in v["by_name"].items()}}
+                             for row, v in trace.summary().items()}
     status = agreed_status()
     assert status == 0, f"a kernel reported wait timeout {status}"
     if rank == 0:

@@ -66,3 +66,42 @@ def test_peer_workspace_addressing():
             assert start % (16 * 32 * 4) == 0 and start + 16 * 32 * 4 <= ws.h8_off
             assert start not in seen
             seen.add(start)
+
+
+def test_stream_trace_bookkeeping():
+    """StreamTrace with injected events: spans land on their rows with the right offsets and durations,
+    and the summary adds up (the real events are CUDA events; only the arithmetic is checked here)."""
+    from torch_int.models.tensor_parallel import StreamTrace, TensorParallel
+
+    class Clock:
+        now = 0.0
+
+    class Event:
+        def record(self, stream):
+            self.t = Clock.now
+
+        def elapsed_time(self, other):      # milliseconds, like torch.cuda.Event
+            return other.t - self.t
+
+    tr = StreamTrace(new_event=Event)
+    tp = TensorParallel(2, 0)
+    assert tp.trace is None
+    with tp.span("ignored", "compute", None):      # tracing off: a no-op context
+        Clock.now += 5.0
+    tp.trace = tr
+    Clock.now = 10.0
+    with tp.span("gemm", "compute", None, group=0):
+        Clock.now += 2.0
+    with tp.span("push", "exchange", None, group=0):
+        Clock.now += 0.5
+    with tp.span("gemm", "compute", None, group=1):
+        Clock.now += 1.0
+    ev = [e for e in tr.events(pid=3) if e["ph"] == "X"]
+    assert [(e["name"], e["tid"], round(e["ts"]), round(e["dur"])) for e in ev] == [
+        ("gemm", 0, 0, 2000), ("push", 1, 2000, 500), ("gemm", 0, 2500, 1000)]
+    assert all(e["pid"] == 3 for e in ev) and ev[0]["args"] == {"group": 0}
+    names = {e["tid"]: e["args"]["name"] for e in tr.events() if e["ph"] == "M"}
+    assert names == {0: "compute", 1: "exchange"}
+    s = tr.summary()
+    assert round(s["compute"]["busy_us"]) == 3000 and round(s["compute"]["last_us"]) == 3500
+    assert round(s["exchange"]["by_name"]["push"]) == 500

@@ -513,27 +513,46 @@ class Int8OPTDecoder(nn.Module):
             ready[c].record(compute)
         comm.wait_stream(compute)
 
-        def exchange(c, scale, bias, ln):
-            """On the communication stream.  Peer-memory form: the GEMM epilogue has already
-            stored this rank's partial sums into the owners' stage slabs; barrier, then one kernel
-            sums the slabs of my rows, applies scale/bias/residual/LayerNorm/quantise and stores the
-            int8 rows into every rank's activation buffer; barrier.  NCCL form: reduce-scatter ->
-            fused LayerNorm kernel -> all-gather."""
+        # with a second communication stream the reduction of one group overlaps the copies of the next
+        comm2 = tp.comm_stream(dev, 1) if (ws is not None and tp.comm_streams > 1) else comm
+        copied = [torch.cuda.Event() for _ in range(chunks)] if comm2 is not comm else None
+        if comm2 is not comm:
+            comm2.wait_stream(compute)
+            for c in range(chunks):
+                res[c].record_stream(comm2)
+
+        def exchange(c, scale, bias, ln, tag):
+            """On the communication stream(s).  Peer-memory form: this rank's partial sums go into
+            the owners' stage slabs (copy engines, or already stored there by the GEMM epilogue);
+            barrier; one kernel sums the slabs of my rows, applies scale/bias/residual/LayerNorm/
+            quantise and stores the int8 rows into every rank's activation buffer; barrier.
+            NCCL form: reduce-scatter -> fused LayerNorm kernel -> all-gather."""
             done[c].record(compute)
             with torch.cuda.stream(comm):
                 comm.wait_event(done[c])
                 if ws is not None:
-                    if tp.peer_mode == "copy":
-                        ws.push_partials(c, acc[c])
-                    ws.barrier()
-                    res[c] = C.tp_reduce_layernorm_q(ws.stage[c], n, ms * e, scale, bias, res[c], ln.weight,
-                                                     ln.bias, ln.eps, ws.q_dst_ptrs(c), rank * ms)
-                    ws.barrier()
+                    with tp.span("push+barrier", "exchange.copy", comm, group=c, at=tag):
+                        if tp.peer_mode == "copy":
+                            ws.push_partials(c, acc[c])
+                        ws.barrier(0)
+                    if comm2 is not comm:
+                        copied[c].record(comm)
                 else:
-                    shard = tp.reduce_scatter_int32(acc[c])
-                    res[c], q = C.dq_add_layernorm_q_bias(shard, scale, bias, res[c], ln.weight, ln.bias, ln.eps)
-                    tp.all_gather_into(h8[c].view(mc, e), q)
-                ready[c].record(comm)
+                    with tp.span("nccl", "exchange.copy", comm, group=c, at=tag):
+                        shard = tp.reduce_scatter_int32(acc[c])
+                        res[c], q = C.dq_add_layernorm_q_bias(shard, scale, bias, res[c], ln.weight, ln.bias, ln.eps)
+                        tp.all_gather_into(h8[c].view(mc, e), q)
+                    ready[c].record(comm)
+            if ws is not None:
+                with torch.cuda.stream(comm2):
+                    if comm2 is not comm:
+                        comm2.wait_event(copied[c])
+                    with tp.span("reduce+ln", "exchange.reduce", comm2, group=c, at=tag):
+                        res[c] = C.tp_reduce_layernorm_q(ws.stage[c], n, ms * e, scale, bias, res[c], ln.weight,
+                                                         ln.bias, ln.eps, ws.q_dst_ptrs(c), rank * ms)
+                    with tp.span("barrier", "exchange.reduce", comm2, group=c, at=tag):
+                        ws.barrier(1 if comm2 is not comm else 0)
+                    ready[c].record(comm2)
 
         def row_parallel(c, x2d, weight, k):
             """int32 partial sums of a row-parallel linear for chunk c: to the owners' stage slabs
@@ -549,19 +568,24 @@ class Int8OPTDecoder(nn.Module):
             attn = layer.self_attn
             for c in range(chunks):
                 compute.wait_event(ready[c])
-                m = None if mask is None else mask[c * bc:(c + 1) * bc]
-                ctx = attn.forward_fused(h8[c], cache, i, past_len, m, b0=c * bc, context_only=True)
-                row_parallel(c, ctx.view(mc, attn.local_dim), attn.out_proj.weight, attn.local_dim)
-                exchange(c, attn.out_proj._scalar("a"), attn.out_proj.bias, layer.final_layer_norm)
+                with tp.span("attention+out_proj", "compute", compute, group=c, layer=i):
+                    m = None if mask is None else mask[c * bc:(c + 1) * bc]
+                    ctx = attn.forward_fused(h8[c], cache, i, past_len, m, b0=c * bc, context_only=True)
+                    row_parallel(c, ctx.view(mc, attn.local_dim), attn.out_proj.weight, attn.local_dim)
+                exchange(c, attn.out_proj._scalar("a"), attn.out_proj.bias, layer.final_layer_norm, f"{i}.attn")
             next_ln = layers[i + 1].self_attn_layer_norm if i + 1 < nl else layer._identity_ln(dev)
             for c in range(chunks):
                 compute.wait_event(ready[c])
-                f8 = layer.fc1._op(h8[c].view(mc, e))
-                row_parallel(c, f8, layer.fc2.weight, layer.local_ffn)
-                exchange(c, layer.fc2._scalar("a"), layer.fc2.bias, next_ln)
+                with tp.span("fc1+fc2", "compute", compute, group=c, layer=i):
+                    f8 = layer.fc1._op(h8[c].view(mc, e))
+                    row_parallel(c, f8, layer.fc2.weight, layer.local_ffn)
+                exchange(c, layer.fc2._scalar("a"), layer.fc2.bias, next_ln, f"{i}.ffn")
         out = torch.empty((bsz, tgt_len, e), dtype=torch.float32, device=dev)
+        comm.wait_stream(comm2)
         with torch.cuda.stream(comm):
             for c in range(chunks):
+                if comm2 is not comm:
+                    res[c].record_stream(comm)  # allocated on the second stream, last read on this one
                 tp.all_gather_into(out[c * bc:(c + 1) * bc].view(mc, e), res[c])
         compute.wait_stream(comm)
         return out

@@ -10,11 +10,73 @@ epilogue (scale, bias, residual add, LayerNorm, quantise) then runs once on the
 reduced value on every rank.  The reference has no multi-GPU path
 (no torch.distributed call in torch_int/); this file is new functionality.
 """
+import contextlib
+import json
 import os
 from typing import Dict, Optional
 
 import torch
 import torch.distributed as dist
+
+
+class StreamTrace:
+    """Timeline of the pipelined layer loop: named spans bracketed by CUDA events on the stream they
+    run on (an event costs no synchronisation and no launch).  dump() resolves the events after a
+    device synchronise and writes Chrome trace-event JSON (chrome://tracing, Perfetto), one row per
+    stream, so exposed exchange time and idle gaps of the compute stream can be read off directly.
+    `new_event` is injectable so that the bookkeeping can be tested without a GPU."""
+
+    def __init__(self, new_event=None):
+        self._new_event = new_event or (lambda: torch.cuda.Event(enable_timing=True))
+        self.spans = []       # (name, row, args, start event, end event)
+        self.origin = None    # (stream, event) recorded by the first span
+
+    @contextlib.contextmanager
+    def span(self, name: str, row: str, stream, **args):
+        start, end = self._new_event(), self._new_event()
+        start.record(stream)
+        if self.origin is None:
+            self.origin = start
+        try:
+            yield
+        finally:
+            end.record(stream)
+            self.spans.append((name, row, args, start, end))
+
+    def events(self, pid: int = 0):
+        """Chrome trace events (microseconds from the first span's start).  Call after a synchronise."""
+        rows = {}
+        out = []
+        for name, row, args, start, end in self.spans:
+            tid = rows.setdefault(row, len(rows))
+            ts = self.origin.elapsed_time(start) * 1e3
+            out.append({"name": name, "ph": "X", "pid": pid, "tid": tid, "ts": ts,
+                        "dur": max(0.0, start.elapsed_time(end) * 1e3), "args": args})
+        for row, tid in rows.items():
+            out.append({"name": "thread_name", "ph": "M", "pid": pid, "tid": tid, "args": {"name": row}})
+        return out
+
+    def summary(self):
+        """Per row: busy microseconds (sum of span durations) and the extent from first start to last end."""
+        acc = {}
+        for e in self.events():
+            if e["ph"] != "X":
+                continue
+            r = acc.setdefault(e["tid"], {"busy_us": 0.0, "first_us": e["ts"], "last_us": e["ts"] + e["dur"],
+                                          "by_name": {}})
+            r["busy_us"] += e["dur"]
+            r["first_us"] = min(r["first_us"], e["ts"])
+            r["last_us"] = max(r["last_us"], e["ts"] + e["dur"])
+            r["by_name"][e["name"]] = r["by_name"].get(e["name"], 0.0) + e["dur"]
+        names = {e["tid"]: e["args"]["name"] for e in self.events() if e["ph"] == "M"}
+        return {names[t]: v for t, v in acc.items()}
+
+    def dump(self, path: str, pid: int = 0):
+        with open(path, "w") as f:
+            json.dump({"traceEvents": self.events(pid), "summary": self.summary()}, f)
+
+
+_NO_SPAN = contextlib.nullcontext()
 
 
 class TensorParallel:
@@ -38,6 +100,16 @@ class TensorParallel:
         self.peer_mode = os.environ.get("TI_TP_PEER_MODE", "copy")
         # SMs the GEMM grids may use while exchanges overlap them (0 = all); TI_TP_GEMM_SMS overrides
         self.gemm_sm_limit = int(os.environ.get("TI_TP_GEMM_SMS", "0"))
+        # 1: one communication stream carries copy -> barrier -> reduce+LayerNorm -> barrier of each
+        # exchange back to back.  2: the copies (+ first barrier) and the reduce kernel (+ second barrier)
+        # run on two streams, so the copies of the next group overlap the reduction of this one.
+        self.comm_streams = int(os.environ.get("TI_TP_COMM_STREAMS", "1"))
+        # a StreamTrace while a forward pass is being traced, else None
+        self.trace: Optional[StreamTrace] = None
+
+    def span(self, name: str, row: str, stream, **args):
+        """Context manager: a span of the timeline when tracing is on, otherwise nothing."""
+        return self.trace.span(name, row, stream, **args) if self.trace is not None else _NO_SPAN
 
     @staticmethod
     def single() -> "TensorParallel":
@@ -59,9 +131,9 @@ class TensorParallel:
         dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
         return partial
 
-    def comm_stream(self, device):
-        """The stream the exchanges of the pipelined layer loop are enqueued on."""
-        key = torch.device(device).index
+    def comm_stream(self, device, index: int = 0):
+        """The stream(s) the exchanges of the pipelined layer loop are enqueued on."""
+        key = (torch.device(device).index, index)
         if key not in self._comm_streams:
             self._comm_streams[key] = torch.cuda.Stream(device=device)
         return self._comm_streams[key]
@@ -197,8 +269,11 @@ class PeerWorkspace:
         self.buf[self.pad_off:].zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)  # every rank's pads are zero before the first barrier kernel
-        self.epoch = 0
-        self.pad_ptrs = [p + self.pad_off for p in self.ptrs]
+        # four independent barrier channels of 64 bytes (up to 16 ranks) each, with their own epochs:
+        # barriers issued on different streams must not share words
+        self.epochs = [0] * 4
+        self.channel_pads = [[p + self.pad_off + 64 * ch for p in self.ptrs] for ch in range(4)]
+        self.pad_ptrs = self.channel_pads[0]
         # Preflight: a few barriers over the fresh pads.  If peer stores or loads do not work on this
         # machine the (bounded) waits give up and set the status word; every rank then learns of it
         # through one NCCL reduction and the caller falls back to NCCL collectives.
@@ -227,6 +302,8 @@ class PeerWorkspace:
             o = (r + 1 + i) % self.tp.size  # start with the right-hand neighbour: spreads the link load
             self.peer_stage[o][c, r].copy_(acc[o * ms:(o + 1) * ms], non_blocking=True)
 
-    def barrier(self):
-        self.epoch += 1
-        self._C.tp_barrier(self.pad_ptrs, self.tp.rank, self.epoch, self.device)
+    def barrier(self, channel: int = 0):
+        """Enqueues a bounded barrier over all ranks on the current stream.  All barriers of one
+        channel must be issued from one stream, in the same order on every rank."""
+        self.epochs[channel] += 1
+        self._C.tp_barrier(self.channel_pads[channel], self.tp.rank, self.epochs[channel], self.device)
