@@ -223,6 +223,23 @@ int ti_decode_attention_s8(const int8_t* qkv, int64_t ld_qkv, int8_t* keys, int8
                            float alpha_qk, float alpha_pv, int8_t* ctx, int64_t ld_ctx, void* stream);
 int ti_advance_position(int32_t* position, int32_t by, void* stream);
 
+/* Causal prefill attention in ONE kernel (scores, softmax and context never leave the SM):
+ *   s_tj = alpha_qk * float(q_t . k_j),  p_tj = int8(rne(127 * softmax_j(s_tj)))  over j <= t + (S - T),
+ *   ctx_t = sat_rne(alpha_pv * float(sum_j p_tj * v_j))
+ * for `batch` sequences of T query rows and S >= T keys (S - T of them cached), `heads` heads of head_dim
+ * 64 or 128.  Strides in bytes: query row t of sequence b, head h at q + b*q_batch_stride + t*ld_q +
+ * h*head_dim; key rows likewise; vt = [batch][heads][head_dim][ld_vt] with the keys contiguous (the
+ * transposed value cache); ctx row at ctx + b*ctx_batch_stride + t*ld_ctx + h*head_dim.  All pointers and
+ * strides multiples of 16.  No additive mask: callers with padding masks use ti_gemm_i8_ex + ti_softmax_q.
+ * Replaces bmm_s8t_s8n_f32t -> mask/softmax/x127/round -> bmm_s8t_s8n_s8t of Int8OPTAttention.forward
+ * (torch_int/models/opt.py:131-181).  Rounding: the row sum is accumulated tile by tile, so p may differ
+ * from the three-kernel path by one unit on rounding ties.
+ * STATUS: compiled for sm_100a but not yet run on hardware; nothing in the library calls it by default. */
+int ti_attention_prefill_s8(const int8_t* q, int64_t ld_q, int64_t q_batch_stride, const int8_t* k, int64_t ld_k,
+                            int64_t k_batch_stride, const int8_t* vt, int64_t ld_vt, int8_t* ctx, int64_t ld_ctx,
+                            int64_t ctx_batch_stride, int64_t batch, int64_t heads, int64_t head_dim, int64_t T,
+                            int64_t S, float alpha_qk, float alpha_pv, void* stream);
+
 /* ---- status ---- */
 
 /* Message of the last error raised on the calling thread ("" if none). */

@@ -3,6 +3,7 @@
 // launcher; nothing here allocates or synchronises.
 #include "../../include/torch_int_b200.h"
 
+#include "attention_prefill.h"
 #include "gemm_i8.h"
 #include "norm_quant.h"
 
@@ -204,6 +205,32 @@ int ti_decode_attention_s8(const int8_t* qkv, int64_t ld_qkv, int8_t* keys, int8
 
 int ti_advance_position(int32_t* position, int32_t by, void* stream) {
   return advance_position(position, by, static_cast<cudaStream_t>(stream));
+}
+
+int ti_attention_prefill_s8(const int8_t* q, int64_t ld_q, int64_t q_batch_stride, const int8_t* k, int64_t ld_k,
+                            int64_t k_batch_stride, const int8_t* vt, int64_t ld_vt, int8_t* ctx, int64_t ld_ctx,
+                            int64_t ctx_batch_stride, int64_t batch, int64_t heads, int64_t head_dim, int64_t T,
+                            int64_t S, float alpha_qk, float alpha_pv, void* stream) {
+  AttnProblem a;
+  a.q = q;
+  a.k = k;
+  a.vt = vt;
+  a.ctx = ctx;
+  a.batch = batch;
+  a.heads = heads;
+  a.head_dim = head_dim;
+  a.T = T;
+  a.S = S;
+  a.ld_q = ld_q;
+  a.q_batch_stride = q_batch_stride;
+  a.ld_k = ld_k;
+  a.k_batch_stride = k_batch_stride;
+  a.ld_vt = ld_vt;
+  a.ld_ctx = ld_ctx;
+  a.ctx_batch_stride = ctx_batch_stride;
+  a.alpha_qk = alpha_qk;
+  a.alpha_pv = alpha_pv;
+  return attention_prefill_s8(a, static_cast<cudaStream_t>(stream));
 }
 
 const char* ti_last_error(void) { return last_error(); }

@@ -62,6 +62,13 @@ int64_t split_k_workspace_bytes(int64_t M, int64_t N);
 // Caps the number of SMs the persistent GEMM grids use (0 = all SMs of the device).
 void set_sm_limit(int sms);
 
+// Tensor map (CUtensorMap, 128 bytes, passed as an opaque pointer so that this header needs no
+// driver API types) of a K-major int8 operand [batch2, batch, rows, K]: box = 128 bytes of K x
+// box_rows x 1 x 1, 128-byte swizzle, out-of-range elements read as zero.  A batch index of extent
+// 1 or stride 0 becomes a dimension of extent 1.  Returns false after set_error().
+bool make_operand_map(void* tensor_map, const int8_t* ptr, int64_t K, int64_t rows, int64_t batch,
+                      int64_t batch2, int64_t ld, int64_t stride, int64_t stride2, int box_rows);
+
 // Status word set by kernels whose bounded waits gave up (0 = ok).
 int* status_word_ptr();
 int device_status(int* status, bool reset);

@@ -585,10 +585,13 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+}  // namespace
+
 // K-major int8 operand [batch2, batch, rows, K] -> 4-D tensor map with a
 // (128 bytes of K) x box_rows x 1 x 1 box, 128-byte swizzle, zero fill.
-bool make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t K, int64_t rows, int64_t batch,
+bool make_operand_map(void* tensor_map, const int8_t* ptr, int64_t K, int64_t rows, int64_t batch,
                       int64_t batch2, int64_t ld, int64_t stride, int64_t stride2, int box_rows) {
+  CUtensorMap* map = static_cast<CUtensorMap*>(tensor_map);
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) {
     set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -622,6 +625,8 @@ bool make_operand_map(CUtensorMap* map, const int8_t* ptr, int64_t K, int64_t ro
   }
   return true;
 }
+
+namespace {
 
 // Upper bound on the SMs the persistent GEMM grid occupies (0 = all).  A caller that
 // overlaps collectives with the GEMMs lowers it so that the collective's CTAs find free SMs.

@@ -18,8 +18,12 @@ namespace ti {
 
 // Device-global status word: 0 = ok, otherwise the code of the first wait
 // that gave up (see the TI_ERR_* values).  Read by ti_device_status().
-// Defined here, so this header belongs in exactly one translation unit.
+// Defined here, so exactly one translation unit includes this header plainly; any other one
+// defines TI_PTX_EXTERNAL_STATUS first, gets no definition, receives the word's address as a
+// kernel argument and waits with mbar_wait_status().
+#ifndef TI_PTX_EXTERNAL_STATUS
 __device__ int ti_kernel_status = 0;
+#endif
 
 enum : int {
   TI_ERR_WAIT_EMPTY = 101,       // producer waited for a free smem stage
@@ -125,6 +129,28 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return ok != 0;
 }
 
+// Bounded wait that reports through a status word given by address (see TI_PTX_EXTERNAL_STATUS).
+__device__ __forceinline__ bool mbar_wait_status(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                 int* status, int err_code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > TI_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, err_code);
+        return false;
+      }
+    }
+  }
+}
+
+#ifndef TI_PTX_EXTERNAL_STATUS
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by all
 // roles of the CTA: once one wait gives up, all later waits return at once.
 template <bool kCluster = false>
@@ -147,6 +173,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+#endif  // TI_PTX_EXTERNAL_STATUS
 
 // ---------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {

@@ -100,6 +100,9 @@ _c_tp_barrier = _sig("ti_tp_barrier", [ctypes.POINTER(_ptr), _i32, _i32, ctypes.
 _c_decode_attention = _sig("ti_decode_attention_s8",
                            [_ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _f32, _f32, _ptr, _i64, _ptr])
 _c_advance_position = _sig("ti_advance_position", [_ptr, _i32, _ptr])
+_c_attention_prefill = _sig("ti_attention_prefill_s8",
+                            [_ptr, _i64, _i64, _ptr, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64,
+                             _i64, _i64, _i64, _i64, _i64, _f32, _f32, _ptr])
 _c_transpose_values = _sig("ti_transpose_values", [_ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _ptr])
 _c_last_error = _sig("ti_last_error", [], ctypes.c_char_p)
 _c_device_status = _sig("ti_device_status", [ctypes.POINTER(ctypes.c_int), _i32])
@@ -521,6 +524,26 @@ def decode_attention(qkv, keys, values_t, position, alpha_qk, alpha_pv):
                                  _stream_ptr(qkv.device))
     _check(rc)
     return ctx
+
+
+def attention_prefill(q, k_rows, vt, out, *, batch, heads, head_dim, tgt_len, src_len, ld_q, q_batch_stride,
+                      ld_k, k_batch_stride, ld_vt, alpha_qk, alpha_pv):
+    """Causal prefill attention in one kernel (ti_attention_prefill_s8): int8 views q (query rows, row
+    stride ld_q, head h at column h*head_dim), k_rows (key rows) and vt ([batch, heads, head_dim, ld_vt],
+    keys contiguous) -> int8 context written into out [batch, tgt_len, heads*head_dim].  Row t sees keys
+    j <= t + (src_len - tgt_len).  Not yet run on hardware: callers opt in explicitly."""
+    for t, name in ((q, "q"), (k_rows, "k_rows"), (vt, "vt"), (out, "out")):
+        if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.int8):
+            raise RuntimeError(f"{name} must be a CUDA int8 tensor")
+    el = heads * head_dim
+    if out.shape != (batch, tgt_len, el) or not out.is_contiguous():
+        raise RuntimeError(f"out must be a contiguous [{batch}, {tgt_len}, {el}] tensor, got {tuple(out.shape)}")
+    with _on_device(q.device):
+        rc = _c_attention_prefill(q.data_ptr(), ld_q, q_batch_stride, k_rows.data_ptr(), ld_k, k_batch_stride,
+                                  vt.data_ptr(), ld_vt, out.data_ptr(), el, tgt_len * el, batch, heads, head_dim,
+                                  tgt_len, src_len, float(alpha_qk), float(alpha_pv), _stream_ptr(q.device))
+    _check(rc)
+    return out
 
 
 def advance_position(position, by=1):

@@ -31,6 +31,7 @@ before the fused residual/LayerNorm kernel, so every rank count gives
 bit-identical results.
 """
 import math
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
@@ -85,6 +86,10 @@ class Int8OPTAttention(nn.Module):
         self.local_heads = num_heads // self.tp.size
         self.local_dim = self.local_heads * self.head_dim
         self.attention_weight_scale = 1.0
+        # Run the causal prefill attention as one fused kernel (C.attention_prefill) instead of
+        # scores GEMM -> softmax -> context GEMM.  Off by default: the fused kernel has not been run
+        # on hardware yet; TI_FUSED_ATTENTION=1 or setting the attribute turns it on.
+        self.fused_attention = os.environ.get("TI_FUSED_ATTENTION", "0") == "1"
         self.qk_bmm = BMM_S8T_S8N_F32T(1.0)
         self.pv_bmm = BMM_S8T_S8N_S8T(1.0)
         # column-parallel: each rank owns whole heads
@@ -152,6 +157,13 @@ class Int8OPTAttention(nn.Module):
         Returns int8 [B,T,Hl*D]."""
         hl, d, el = self.local_heads, self.head_dim, self.local_dim
         dev = q.device
+        if self.fused_attention and mask is None and causal >= 0 and d in (64, 128):
+            # one kernel; scores and probabilities stay on the SM (opt-in: see fused_attention)
+            out = torch.empty((bsz, tgt_len, el), dtype=torch.int8, device=dev)
+            return C.attention_prefill(q, k_rows, vt, out, batch=bsz, heads=hl, head_dim=d, tgt_len=tgt_len,
+                                       src_len=src_len, ld_q=q_row_stride, q_batch_stride=tgt_len * q_row_stride,
+                                       ld_k=k_row_stride, k_batch_stride=k_batch_stride, ld_vt=vt_row_stride,
+                                       alpha_qk=self.qk_bmm._alpha(), alpha_pv=self.pv_bmm._alpha())
         scores = torch.empty((bsz * hl, tgt_len, src_pad), dtype=torch.float32, device=dev)
         C.gemm_i8_ex(q, k_rows, scores, epilogue=C.EPI_F32_ALPHA, m=tgt_len, n=src_pad, k=d,
                      batch=hl, batch2=bsz, lda=q_row_stride, ldb=k_row_stride, ldc=src_pad,
