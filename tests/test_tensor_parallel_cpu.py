@@ -83,6 +83,14 @@ def _rank_main(rank, world, port, ret):
             tp.all_reduce_int32(torch.zeros(4))
         except RuntimeError:
             refused = True
+        # vocabulary-parallel language-model head: every rank multiplies with its rows of the tied
+        # embedding table; the gathered logits equal the whole product (same dot products, fp32)
+        table = full["model.decoder.embed_tokens.weight"]
+        whole = torch.nn.functional.linear(residual, table)
+        split = tp.vocab_parallel_logits(residual, table)
+        ok = ok and split.shape == whole.shape and torch.allclose(split, whole, rtol=1e-5, atol=1e-5)
+        odd = torch.randn((world * 3 + 1, e), generator=g)       # a vocabulary that does not divide: whole product
+        ok = ok and torch.equal(tp.vocab_parallel_logits(residual, odd), torch.nn.functional.linear(residual, odd))
         ret[rank] = (ok, refused, float((residual - want).abs().max()))
     finally:
         dist.destroy_process_group()

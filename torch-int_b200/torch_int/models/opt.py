@@ -794,14 +794,20 @@ class Int8OPTForCausalLM(nn.Module):
         hidden = out.last_hidden_state
         if last_token_only:
             hidden = hidden[:, -1:, :]
-        logits = self.lm_head(hidden.to(self.lm_head.weight.dtype)).contiguous()
-        return CausalLMOutput(logits, out.past_key_values)
+        return CausalLMOutput(self._logits(hidden).contiguous(), out.past_key_values)
+
+    def _logits(self, hidden):
+        hidden = hidden.to(self.lm_head.weight.dtype)
+        tp = self.model.decoder.tp
+        if tp.size > 1 and tp.vocab_parallel and self.lm_head.bias is None:
+            return tp.vocab_parallel_logits(hidden, self.lm_head.weight)
+        return self.lm_head(hidden)
 
     @torch.no_grad()
     def decode_step(self, tokens, cache: StaticInt8KVCache):
         """Logits [B, vocab] of the token after `tokens` [B,1], appended to `cache`."""
         hidden = self.model.decoder.decode_step(tokens, cache)
-        return self.lm_head(hidden[:, -1, :].to(self.lm_head.weight.dtype))
+        return self._logits(hidden[:, -1, :])
 
     @torch.no_grad()
     def generate_greedy(self, input_ids, max_new_tokens: int, cache: Optional[StaticInt8KVCache] = None,

@@ -106,6 +106,11 @@ class TensorParallel:
         self.comm_streams = int(os.environ.get("TI_TP_COMM_STREAMS", "1"))
         # a StreamTrace while a forward pass is being traced, else None
         self.trace: Optional[StreamTrace] = None
+        # language-model head split by vocabulary rows: each rank multiplies with its 1/size of the
+        # (tied, replicated) embedding table and the logits are all-gathered.  The floating-point GEMM
+        # of a shard may round differently from the whole one, so logits are then equal to the
+        # single-GPU ones only to fp32 / fp16 accuracy, not bit for bit: opt-in (TI_TP_VOCAB_PARALLEL=1).
+        self.vocab_parallel = os.environ.get("TI_TP_VOCAB_PARALLEL", "0") == "1"
 
     def span(self, name: str, row: str, stream, **args):
         """Context manager: a span of the timeline when tracing is on, otherwise nothing."""
@@ -161,6 +166,22 @@ class TensorParallel:
         """Concatenates the ranks' row shards into `full` (rank order)."""
         dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
         return full
+
+    def vocab_parallel_logits(self, hidden: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        """hidden [..., E] x table[V, E]^T -> logits [..., V], each rank computing the columns of its
+        V/size rows of `table` (a view: the table stays whole and tied to the embedding) followed by an
+        all-gather.  Falls back to the whole product when V does not divide over the ranks."""
+        v = table.shape[0]
+        if self.size == 1 or v % self.size != 0:
+            return torch.nn.functional.linear(hidden, table)
+        v0, v1 = self.shard_range(v)
+        lead = hidden.shape[:-1]
+        local = torch.nn.functional.linear(hidden.reshape(-1, hidden.shape[-1]), table[v0:v1])   # [tokens, V/size]
+        tokens = local.shape[0]
+        gathered = torch.empty((self.size * tokens, v1 - v0), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(gathered, local.contiguous(), group=self.group)   # rank blocks along dim 0
+        # [size, tokens, V/size] -> [tokens, size * V/size]
+        return gathered.view(self.size, tokens, v1 - v0).permute(1, 0, 2).reshape(*lead, v)
 
     def peer_workspace(self, chunks: int, mc: int, e: int, device):
         """Peer-accessible buffers for the fused exchange of the pipelined layer loop, or
