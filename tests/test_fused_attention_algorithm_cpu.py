@@ -46,7 +46,8 @@ def emulate(q, k, vt, past, alpha_qk, alpha_pv):
             tmax = np.where(vis, s, fmin).max(axis=1).astype(F)
             mn = np.maximum(m, tmax)
             l = (l * np.exp((m - mn).astype(F)).astype(F)).astype(F)
-            e = np.where(vis, np.exp((s - mn[:, None]).astype(F)), F(0)).astype(F)
+            with np.errstate(over="ignore"):             # rows past the end (nothing visible): masked by `vis`
+                e = np.where(vis, np.exp((s - mn[:, None]).astype(F)), F(0)).astype(F)
             l = (l + e.sum(axis=1, dtype=F)).astype(F)
             m = mn
         acc_o = np.zeros((TILE, d), dtype=np.int64)
