@@ -94,3 +94,19 @@ def test_no_cpu_fallback():
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         _CUDA.dq_add_layernorm_q(torch.zeros((2, 16), dtype=torch.int32), 0.1, torch.zeros(2, 16),
                                  torch.ones(16), torch.zeros(16), 1e-5)
+
+
+def test_lm_head_logits_helper_on_cpu():
+    """Int8OPTForCausalLM._logits is plain torch: tied table, cast to the table's dtype, and the
+    vocabulary-parallel form only when a tensor-parallel context asks for it."""
+    from torch_int.models.opt import Int8OPTConfig
+    from torch_int.models.random_init import random_int8_opt
+    cfg = Int8OPTConfig(vocab_size=48, hidden_size=32, num_hidden_layers=1, ffn_dim=64, num_attention_heads=2,
+                        max_position_embeddings=16)
+    model = random_int8_opt(cfg, seed=1, device="cpu")
+    hidden = torch.randn(2, 3, 32, generator=torch.Generator().manual_seed(2))
+    want = torch.nn.functional.linear(hidden, model.model.decoder.embed_tokens.weight)
+    assert torch.equal(model._logits(hidden), want)
+    assert torch.equal(model._logits(hidden.double()), want)          # cast to the table's dtype first
+    attn = model.model.decoder.layers[0].self_attn
+    assert attn.fused_attention is False                              # the unvalidated fused kernel is opt-in

@@ -593,7 +593,8 @@ class Int8OPTDecoder(nn.Module):
                     row_parallel(c, f8, layer.fc2.weight, layer.local_ffn)
                 exchange(c, layer.fc2._scalar("a"), layer.fc2.bias, next_ln, f"{i}.ffn")
         out = torch.empty((bsz, tgt_len, e), dtype=torch.float32, device=dev)
-        comm.wait_stream(comm2)
+        if comm2 is not comm:
+            comm.wait_stream(comm2)
         with torch.cuda.stream(comm):
             for c in range(chunks):
                 if comm2 is not comm:
