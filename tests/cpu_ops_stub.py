@@ -131,3 +131,53 @@ def advance_position(position, by=1):
 
 def device_status(reset=False):
     return 0
+
+
+# ----------------------------------------------------------------------------- installation
+def install(setattr_fn=setattr):
+    """Puts this module in place of torch_int._CUDA inside torch_int.models / torch_int.nn.  `setattr_fn`
+    is monkeypatch.setattr in a pytest process (undone at teardown) or plain setattr in a child process."""
+    import sys
+    import torch_int.models.kv_cache as kv_mod
+    import torch_int.models.opt as opt_mod
+    import torch_int.nn.bmm as bmm_mod
+    import torch_int.nn.fused as fused_mod
+    import torch_int.nn.linear as linear_mod
+    this = sys.modules[__name__]
+    setattr_fn(opt_mod, "C", this)
+    setattr_fn(kv_mod, "C", this)
+    for mod in (linear_mod, bmm_mod, fused_mod):
+        for name in dir(this):
+            if not name.startswith("_") and callable(getattr(this, name)) and hasattr(mod, name):
+                setattr_fn(mod, name, getattr(this, name))
+
+
+class _NoStream:
+    """Stand-in for torch.cuda.Stream / Event on CPU ranks: everything runs in program order."""
+
+    def __init__(self, *args, **kwargs):
+        pass
+
+    def record(self, stream=None):
+        pass
+
+    def wait_event(self, event):
+        pass
+
+    def wait_stream(self, stream):
+        pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def install_serial_streams(setattr_fn=setattr):
+    """torch.cuda streams and events become no-ops (CPU ranks run the pipelined layer loop in program order)."""
+    setattr_fn(torch.cuda, "current_stream", lambda device=None: _NoStream())
+    setattr_fn(torch.cuda, "Stream", _NoStream)
+    setattr_fn(torch.cuda, "Event", _NoStream)
+    setattr_fn(torch.cuda, "stream", lambda s: _NoStream())
+    setattr_fn(torch.Tensor, "record_stream", lambda self, stream: None)

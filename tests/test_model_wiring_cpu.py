@@ -12,19 +12,9 @@ from oracle import opt_model as OM
 
 @pytest.fixture()
 def cpu_model(monkeypatch):
-    import torch_int.models.kv_cache as kv_mod
-    import torch_int.models.opt as opt_mod
-    import torch_int.nn.bmm as bmm_mod
-    import torch_int.nn.fused as fused_mod
-    import torch_int.nn.linear as linear_mod
     from torch_int.models.opt import Int8OPTConfig
     from torch_int.models.random_init import random_int8_opt
-    monkeypatch.setattr(opt_mod, "C", stub)
-    monkeypatch.setattr(kv_mod, "C", stub)
-    for mod in (linear_mod, bmm_mod, fused_mod):
-        for name in dir(stub):
-            if hasattr(mod, name) and callable(getattr(stub, name)) and not name.startswith("_"):
-                monkeypatch.setattr(mod, name, getattr(stub, name))
+    stub.install(monkeypatch.setattr)
     cfg = Int8OPTConfig(vocab_size=96, hidden_size=128, num_hidden_layers=2, ffn_dim=256, num_attention_heads=2,
                         max_position_embeddings=64)
     model = random_int8_opt(cfg, seed=7, device="cpu")

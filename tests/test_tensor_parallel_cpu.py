@@ -133,3 +133,81 @@ def test_single_rank_context_is_a_no_op():
     assert tp.all_reduce_int32(t) is t
     sd = {"x.q_proj.weight": torch.zeros(4, 4)}
     assert tp.shard_state_dict(sd)["x.q_proj.weight"].shape == (4, 4)
+
+
+# --------------------------------------------------------------------------- the product model on CPU ranks
+def _model_rank_main(rank, world, port, ret):
+    """The PRODUCT's tensor-parallel model code (torch_int.models.opt with a TensorParallel context) on
+    gloo ranks: the extension is replaced by the oracle-backed stand-ins of tests/cpu_ops_stub.py and CUDA
+    streams by no-ops, so the Python of both layer loops runs - the all-reduce form (short inputs, decode
+    steps) and the pipelined reduce-scatter / LayerNorm-on-my-rows / all-gather form with its collective
+    fallback (the peer-memory exchange itself needs GPUs) - and must reproduce the single-rank oracle."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import cpu_ops_stub as stub
+        from torch_int.models.opt import Int8OPTConfig
+        from torch_int.models.random_init import random_int8_opt
+        from torch_int.models.tensor_parallel import TensorParallel
+        torch.set_num_threads(1)
+        stub.install()
+        stub.install_serial_streams()
+        cfg = Int8OPTConfig(vocab_size=64, hidden_size=256, num_hidden_layers=2, ffn_dim=512,
+                            num_attention_heads=4, max_position_embeddings=64)
+        whole = random_int8_opt(cfg, seed=5, device="cpu")                 # the same model, unsplit
+        full_sd = {k: v.detach() for k, v in whole.state_dict().items()}
+        tp = TensorParallel.from_world()
+        tp.use_peer_memory = False
+        model = random_int8_opt(cfg, seed=5, device="cpu", tp=tp)
+        ids = torch.randint(2, 64, (4, 24), generator=torch.Generator().manual_seed(8))
+        want, _ = OM.causal_lm_logits(full_sd, cfg, ids)
+        checks = {}
+        # all-reduce form (fewer tokens than min_pipeline_tokens)
+        assert tp.plan_chunks(4, 24) == 0
+        checks["all_reduce"] = torch.equal(model(ids).logits, want)
+        # pipelined form: 4 sequences -> max_chunks groups; rows per group divisible by the ranks
+        tp.min_pipeline_tokens = 1
+        tp.max_chunks = 2
+        assert tp.plan_chunks(4, 24) == 2
+        checks["pipelined_2_groups"] = torch.equal(model(ids).logits, want)
+        tp.max_chunks = 4
+        assert tp.plan_chunks(4, 24) == 4
+        checks["pipelined_4_groups"] = torch.equal(model(ids).logits, want)
+        # the same with the timeline spans switched on (events are no-ops here; only the plumbing runs)
+        from torch_int.models.tensor_parallel import StreamTrace
+        tp.trace = StreamTrace()
+        checks["traced"] = torch.equal(model(ids).logits, want)
+        names = {(name, row) for name, row, *_ in tp.trace.spans}
+        checks["trace_rows"] = names == {("attention+out_proj", "compute"), ("fc1+fc2", "compute"),
+                                         ("nccl", "exchange.copy")}
+        checks["trace_count"] = len(tp.trace.spans) == 2 * 2 * 4 * 2      # layers x phases x groups x (compute, exchange)
+        tp.trace = None
+        # vocabulary-parallel head on top of the pipelined loop
+        tp.vocab_parallel = True
+        checks["vocab_parallel"] = torch.allclose(model(ids).logits, want, rtol=1e-5, atol=1e-5)
+        tp.vocab_parallel = False
+        # cache + decode steps under tensor parallelism (decode steps use the all-reduce form)
+        dec = model.model.decoder
+        cache = model.new_cache(4, 32)
+        model(ids[:, :20], past_key_values=cache, use_cache=True)
+        step = dec.decode_step(ids[:, 20:21], cache)[:, -1]
+        checks["decode_step"] = torch.equal(step, OM.decoder(full_sd, cfg, ids[:, :21])[0][:, -1])
+        ret[rank] = checks
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_product_model_on_cpu_ranks(world):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_model_rank_main, args=(r, world, port, ret)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=300)
+        assert pr.exitcode == 0, f"rank exited with {pr.exitcode}"
+    for r in range(world):
+        assert all(ret[r].values()), f"rank {r}: {ret[r]}"

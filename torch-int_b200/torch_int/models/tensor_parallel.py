@@ -157,8 +157,13 @@ class TensorParallel:
         """Sum of the ranks' int32 partials [M, E]; rank r receives rows [r*M/n, (r+1)*M/n)."""
         if partial.dtype != torch.int32 or partial.shape[0] % self.size != 0:
             raise RuntimeError("reduce_scatter_int32 needs an int32 tensor whose rows divide evenly over the ranks")
-        out = torch.empty((partial.shape[0] // self.size,) + tuple(partial.shape[1:]), dtype=torch.int32,
-                          device=partial.device)
+        rows = partial.shape[0] // self.size
+        if dist.get_backend(self.group) == "gloo":
+            # CPU ranks (the host-logic tests): gloo has no reduce-scatter; integer sums are exact either way
+            total = partial.clone()
+            dist.all_reduce(total, op=dist.ReduceOp.SUM, group=self.group)
+            return total[self.rank * rows:(self.rank + 1) * rows].contiguous()
+        out = torch.empty((rows,) + tuple(partial.shape[1:]), dtype=torch.int32, device=partial.device)
         dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM, group=self.group)
         return out
 
