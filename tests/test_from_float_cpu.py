@@ -103,6 +103,28 @@ def test_causal_lm_from_float():
     assert float((got.argmax(-1) == want.argmax(-1)).double().mean()) > 0.8
 
 
+def test_converted_model_runs_through_the_product_wiring(monkeypatch):
+    """The modules as from_float leaves them ([N] int8 biases, scales as tensors or Python floats, the float
+    model's embedding modules) go through the product's own forward - fused q/k/v weights, strided attention,
+    fused residual/LayerNorm steps - with the extension replaced by oracle-backed stand-ins, and give exactly
+    the oracle's reference dataflow on the converted state dict."""
+    import cpu_ops_stub as stub
+    from torch_int.models.opt import Int8OPTForCausalLM
+    torch.manual_seed(3)
+    cfg = _config(layers=2)
+    model = OPTForCausalLM(cfg).eval()
+    ids = torch.randint(2, cfg.vocab_size, (2, 19), generator=torch.Generator().manual_seed(4))
+    scales = [_calibrate(layer, lambda: model(ids)) for layer in model.model.decoder.layers]
+    int8_model = Int8OPTForCausalLM.from_float(model, scales)
+    sd = {k: v.detach().clone() for k, v in int8_model.state_dict().items()}
+    stub.install(monkeypatch.setattr)
+    want, _ = OM.causal_lm_logits(sd, cfg, ids)
+    got = int8_model(ids).logits
+    assert torch.equal(got, want)
+    cache = int8_model.new_cache(2, 32)
+    assert torch.equal(int8_model(ids, past_key_values=cache, use_cache=True).logits, want)
+
+
 def test_from_float_model_saves_and_loads(tmp_path):
     """A quantised model as from_float leaves it (transformers' config object, the float embedding modules
     of the source model) goes through save_pretrained / from_pretrained unchanged."""
