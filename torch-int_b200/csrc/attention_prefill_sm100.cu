@@ -384,6 +384,8 @@ int launch(const AttnProblem& a, cudaStream_t stream) {
     set_error("attention_prefill_s8: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
     return TI_E_CUDA;
   }
+  // two CTAs per SM need 2 x 97 KB: ask for the largest shared-memory carve-out (a hint)
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   const dim3 grid(static_cast<unsigned>((a.T + TILE_ROWS - 1) / TILE_ROWS), static_cast<unsigned>(a.heads),
                   static_cast<unsigned>(a.batch));
   kernel<<<grid, ATT_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
