@@ -7,47 +7,45 @@ import torch
 from .._CUDA import dq_add_layernorm_q, layernorm_q
 
 
-class LayerNormQ(torch.nn.Module):
-    """int8 = clamp(round(LayerNorm(x) * weight + bias), -128, 127); the output
-    scale is folded into weight and bias by ``from_float``."""
+class _QuantisingNorm(torch.nn.Module):
+    """State shared by both modules, with the reference's names: fp32 buffers ``weight`` and ``bias``
+    of the affine step (the output scale already divided in), ``eps`` and ``input_scale``."""
 
     def __init__(self, dim, eps=1e-5):
         super().__init__()
-        self.input_scale = 1.0
         self.eps = eps
-        self.register_buffer("weight", torch.ones(dim, dtype=torch.float32))
-        self.register_buffer("bias", torch.zeros(dim, dtype=torch.float32))
+        self.input_scale = 1.0
+        for name, fill in (("weight", 1.0), ("bias", 0.0)):
+            self.register_buffer(name, torch.full((dim,), fill, dtype=torch.float32))
+
+
+class LayerNormQ(_QuantisingNorm):
+    """int8 = clamp(round(LayerNorm(x) * weight + bias), -128, 127); the output
+    scale is folded into weight and bias by ``from_float``."""
 
     def forward(self, x):
-        if x.dtype not in (torch.float32, torch.float16):
-            x = x.to(torch.float32)
-        elif x.dtype == torch.float16 and self.weight.dtype == torch.float32:
-            # The reference casts x to the dtype of the affine parameters first
-            # (nn/fused.py:14); fp16 -> fp32 is exact, so the fp16 kernel path with
-            # fp32 statistics gives the same result without a cast kernel, except
-            # that it would round the LayerNorm output to fp16.  Keep fp32 semantics.
+        # The reference casts x to the dtype of the affine parameters first (nn/fused.py:14), normally
+        # fp32.  The kernel's fp16 input path rounds the LayerNorm output to fp16 before quantising, which
+        # is what the reference computes only when the parameters themselves were cast to fp16; in every
+        # other case the input is widened (fp16 -> fp32 is exact) and the fp32 path runs.
+        keep_half = x.dtype == torch.float16 and self.weight.dtype != torch.float32
+        if x.dtype != torch.float32 and not keep_half:
             x = x.to(torch.float32)
         return layernorm_q(x.contiguous(), self.weight, self.bias, self.eps)
 
     @staticmethod
     def from_float(module: torch.nn.LayerNorm, output_scale: float):
-        assert module.normalized_shape[0] == module.weight.numel()
-        assert module.normalized_shape[0] == module.bias.numel()
-        q = LayerNormQ(module.normalized_shape[0], module.eps)
+        dim = module.normalized_shape[0]
+        if module.weight.numel() != dim or module.bias.numel() != dim:
+            raise AssertionError("LayerNormQ.from_float needs a one-dimensional affine LayerNorm")
+        q = LayerNormQ(dim, module.eps)
         q.weight = (module.weight / output_scale).detach().float()
         q.bias = (module.bias / output_scale).detach().float()
         return q
 
 
-class DQ_Add_LayerNorm_Q(torch.nn.Module):
+class DQ_Add_LayerNorm_Q(_QuantisingNorm):
     """(residual_out, int8) = LayerNormQ(residual + input_scale * int32 input)."""
-
-    def __init__(self, dim, eps=1e-5):
-        super().__init__()
-        self.input_scale = 1.0
-        self.eps = eps
-        self.register_buffer("weight", torch.ones(dim, dtype=torch.float32))
-        self.register_buffer("bias", torch.zeros(dim, dtype=torch.float32))
 
     def forward(self, residual_input_fp, input_int32):
         return dq_add_layernorm_q(input_int32, self.input_scale, residual_input_fp,
