@@ -59,3 +59,33 @@ def test_argument_validation_needs_no_gpu():
     assert rc == -1
     # empty problem: accepted, nothing launched
     assert lib.ti_linear_a8_w8_b8_o8(base, base, base, base, 0, 16, 32, 1.0, 1.0, None) == 0
+
+
+def test_attention_and_row_kernel_validation_needs_no_gpu():
+    """The attention entry points and the row kernels check their arguments on the host as well."""
+    lib = ctypes.CDLL(LIB)
+    lib.ti_last_error.restype = ctypes.c_char_p
+    i64, f32, p = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
+    lib.ti_attention_prefill_s8.argtypes = [p, i64, i64, p, i64, i64, p, i64, p, i64, i64,
+                                            i64, i64, i64, i64, i64, f32, f32, p]
+    buf = ctypes.create_string_buffer(1 << 16)
+    base = (ctypes.addressof(buf) + 63) & ~63
+
+    def attn(q=base, ld_q=256, qbs=256 * 32, k=base, ld_k=256, kbs=256 * 32, vt=base, ld_vt=32, ctx=base, ld_ctx=256,
+             cbs=256 * 32, batch=1, heads=2, d=128, t=32, s=32):
+        return lib.ti_attention_prefill_s8(q, ld_q, qbs, k, ld_k, kbs, vt, ld_vt, ctx, ld_ctx, cbs, batch, heads, d,
+                                           t, s, 1.0, 1.0, None)
+    assert attn(d=96) == -1 and b"head_dim" in lib.ti_last_error()
+    assert attn(t=40, s=32) == -1                                   # fewer keys than query rows
+    assert attn(ld_q=250) == -1 and b"multiples of 16" in lib.ti_last_error()
+    assert attn(q=base + 8) == -1
+    assert attn(ld_k=128) == -1 and b"row stride" in lib.ti_last_error()   # narrower than heads * head_dim
+    assert attn(ld_vt=16) == -1                                      # shorter than the key count
+    assert attn(q=None) == -1
+    assert attn(batch=0) == 0 and attn(t=0, s=0) == 0                # empty: accepted, nothing launched
+    lib.ti_decode_attention_s8.argtypes = [p, i64, p, p, i64, i64, i64, i64, p, f32, f32, p, i64, p]
+    rc = lib.ti_decode_attention_s8(base, 768, base, base, 1, 2, 96, 64, base, 1.0, 1.0, base, 256, None)
+    assert rc == -1 and b"head_dim" in lib.ti_last_error()
+    rc = lib.ti_decode_attention_s8(base, 768, base, base, 1, 2, 128, 60, base, 1.0, 1.0, base, 256, None)
+    assert rc == -1                                                  # capacity not a multiple of 16
+    assert lib.ti_decode_attention_s8(base, 768, base, base, 0, 2, 128, 64, base, 1.0, 1.0, base, 256, None) == 0
