@@ -2,8 +2,8 @@
 
 Run in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /path/to/reference-checkout
-(or set TORCH_INT_REFERENCE to that path)
+    python tests/golden/make_golden.py /path/to/reference-checkout [generator,generator,...]
+(or set TORCH_INT_REFERENCE to that path; the optional list regenerates only those fixtures)
 
 What comes from where:
   * layernorm_q.npz, dq_add_layernorm_q.npz, quantize_absmax.npz: outputs of the
@@ -20,6 +20,8 @@ What comes from where:
     formulas (tests/test_linear_kernels.py:7-84, tests/test_bmm.py:7-30,112-120):
     a float torch.nn.Linear / torch.bmm, then clamp / round as each test does.
     The tolerances of those tests are stored next to each ground truth.
+  * from_float.npz: the conversion code of the reference's own modules (W8A8*Linear.from_float,
+    BMM_*.from_scale, LayerNormQ.from_float) executed on seeded float modules.
 The fixtures travel with the repository; nothing at test time reads the
 reference checkout.
 """
@@ -177,11 +179,64 @@ def gen_bmm_formulas():
          gt_f32=(f * scale).numpy(), gt_s32=f.round().to(torch.int32).numpy())
 
 
+def gen_from_float():
+    """The conversion code of the reference's own modules (torch_int/nn/linear.py:45-57,89-102,161-179,
+    218-229; nn/bmm.py:17-24,39-46; nn/fused.py:20-27) executed on seeded float modules: quantised
+    weights, biases and scale factors.  The float modules are rebuilt for every call because the
+    reference quantises in place (functional/quantization.py:12)."""
+    from torch_int.nn.bmm import BMM_S8T_S8N_F32T, BMM_S8T_S8N_S8T
+    from torch_int.nn.fused import LayerNormQ
+    from torch_int.nn.linear import (W8A8B8O8Linear, W8A8B8O8LinearReLU, W8A8B32O32Linear,
+                                     W8A8BFP32OFP32Linear)
+
+    def float_linear():
+        g = torch.Generator().manual_seed(321)
+        lin = torch.nn.Linear(48, 80)
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(80, 48, generator=g) * 0.2)
+            lin.bias.copy_(torch.randn(80, generator=g) * 0.5)
+        return lin
+
+    out = {"w": float_linear().weight.detach().numpy().copy(), "b": float_linear().bias.detach().numpy().copy(),
+           "input_scale": np.float64(0.037), "output_scale": np.float64(0.052)}
+    with torch.no_grad():
+        for tag, cls in (("b8o8", W8A8B8O8Linear), ("relu", W8A8B8O8LinearReLU), ("b32o32", W8A8B32O32Linear)):
+            m = cls.from_float(float_linear(), 0.037, 0.052)
+            out.update({f"{tag}_weight": m.weight.numpy(), f"{tag}_bias": m.bias.numpy(),
+                        f"{tag}_a": np.float32(float(m.a)), f"{tag}_b": np.float32(float(m.b))})
+        m = W8A8BFP32OFP32Linear.from_float(float_linear(), 0.037)
+        out.update({"bfp32_weight": m.weight.numpy(), "bfp32_bias": m.bias.numpy(), "bfp32_a": np.float32(float(m.a))})
+        out["bmm_s8t_a"] = np.float32(float(BMM_S8T_S8N_S8T.from_scale(1.0 / 127, 0.031, 0.044).a))
+        out["bmm_f32t_a"] = np.float32(float(BMM_S8T_S8N_F32T.from_scale(0.021, 0.017).a))
+        g = torch.Generator().manual_seed(322)
+        ln = torch.nn.LayerNorm(96)
+        ln.weight.copy_(torch.randn(96, generator=g) * 0.1 + 1)
+        ln.bias.copy_(torch.randn(96, generator=g) * 0.1)
+        out.update({"ln_w": ln.weight.detach().numpy().copy(), "ln_b": ln.bias.detach().numpy().copy()})
+        q = LayerNormQ.from_float(ln, 0.061)
+        out.update({"lnq_weight": q.weight.detach().numpy(), "lnq_bias": q.bias.detach().numpy(),
+                    "ln_output_scale": np.float64(0.061), "ln_eps": np.float64(q.eps)})
+    save("from_float.npz", **out)
+
+
+GENERATORS = ("layernorm", "dq_add", "quantize", "bmm_known", "linear_formulas", "bmm_formulas", "from_float")
+
 if __name__ == "__main__":
+    # optional second argument: comma-separated subset of GENERATORS (default: all)
+    only = set(sys.argv[2].split(",")) if len(sys.argv) > 2 else set(GENERATORS)
+    assert only <= set(GENERATORS), f"unknown generator in {only}; choose from {GENERATORS}"
     LayerNormQ, dq_py, qt, qc = import_reference()
-    gen_layernorm(LayerNormQ)
-    gen_dq_add(dq_py)
-    gen_quantize(qt, qc)
-    gen_bmm_known()
-    gen_linear_formulas()
-    gen_bmm_formulas()
+    if "layernorm" in only:
+        gen_layernorm(LayerNormQ)
+    if "dq_add" in only:
+        gen_dq_add(dq_py)
+    if "quantize" in only:
+        gen_quantize(qt, qc)
+    if "bmm_known" in only:
+        gen_bmm_known()
+    if "linear_formulas" in only:
+        gen_linear_formulas()
+    if "bmm_formulas" in only:
+        gen_bmm_formulas()
+    if "from_float" in only:
+        gen_from_float()

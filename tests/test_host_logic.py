@@ -110,3 +110,45 @@ def test_lm_head_logits_helper_on_cpu():
     assert torch.equal(model._logits(hidden.double()), want)          # cast to the table's dtype first
     attn = model.model.decoder.layers[0].self_attn
     assert attn.fused_attention is False                              # the unvalidated fused kernel is opt-in
+
+
+def test_from_float_matches_the_reference_modules(golden_dir):
+    """from_float / from_scale of the modules here against the results of the REFERENCE's own conversion
+    code on the same seeded float modules (tests/golden/from_float.npz, made by make_golden.py): quantised
+    weights and biases identical, scale factors equal to fp32 rounding, and the float module untouched
+    (the reference quantises its argument in place, functional/quantization.py:12)."""
+    import os
+    import numpy as np
+    from torch_int.nn.bmm import BMM_S8T_S8N_F32T, BMM_S8T_S8N_S8T
+    from torch_int.nn.fused import LayerNormQ
+    from torch_int.nn.linear import W8A8B8O8Linear, W8A8B8O8LinearReLU, W8A8B32O32Linear, W8A8BFP32OFP32Linear
+    z = np.load(os.path.join(golden_dir, "from_float.npz"))
+    lin = torch.nn.Linear(48, 80)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(z["w"]))
+        lin.bias.copy_(torch.from_numpy(z["b"]))
+    s_in, s_out = float(z["input_scale"]), float(z["output_scale"])
+
+    def close(a, b):
+        return abs(float(a) - float(b)) <= 2e-7 * abs(float(b))
+
+    for tag, cls in (("b8o8", W8A8B8O8Linear), ("relu", W8A8B8O8LinearReLU), ("b32o32", W8A8B32O32Linear)):
+        m = cls.from_float(lin, s_in, s_out)
+        assert np.array_equal(m.weight.numpy(), z[f"{tag}_weight"]), tag
+        assert np.array_equal(m.bias.numpy().reshape(-1), z[f"{tag}_bias"].reshape(-1)), tag
+        assert m.bias.dtype == torch.from_numpy(z[f"{tag}_bias"]).dtype
+        assert close(m._scalar("a"), z[f"{tag}_a"]) and close(m._scalar("b"), z[f"{tag}_b"]), tag
+    m = W8A8BFP32OFP32Linear.from_float(lin, s_in)
+    assert np.array_equal(m.weight.numpy(), z["bfp32_weight"])
+    assert np.array_equal(m.bias.numpy().reshape(-1), z["bfp32_bias"].reshape(-1)) and m.bias.dtype == torch.float32
+    assert close(m._scalar("a"), z["bfp32_a"])
+    assert np.array_equal(lin.weight.detach().numpy(), z["w"]) and np.array_equal(lin.bias.detach().numpy(), z["b"])
+    assert close(BMM_S8T_S8N_S8T.from_scale(1.0 / 127, 0.031, 0.044)._alpha(), z["bmm_s8t_a"])
+    assert close(BMM_S8T_S8N_F32T.from_scale(0.021, 0.017)._alpha(), z["bmm_f32t_a"])
+    ln = torch.nn.LayerNorm(96)
+    with torch.no_grad():
+        ln.weight.copy_(torch.from_numpy(z["ln_w"]))
+        ln.bias.copy_(torch.from_numpy(z["ln_b"]))
+    q = LayerNormQ.from_float(ln, float(z["ln_output_scale"]))
+    assert np.array_equal(q.weight.numpy(), z["lnq_weight"]) and np.array_equal(q.bias.numpy(), z["lnq_bias"])
+    assert q.eps == float(z["ln_eps"])
