@@ -516,15 +516,14 @@ class BmmWorkload:
                 sc = C.bmm_s8t_s8n_f32t(q, k, 1.0 / 127 ** 2)
                 return C.bmm_s8t_s8n_s8t(C.softmax_q(sc, None, 40, causal=0), vt, 0.01)
             cases[f"S={s}"]["core_3_kernels_ms"] = round(_event_time(three, 10), 4)
-            if os.environ.get("TI_FUSED_ATTENTION") == "1":
-                # ... and as the one fused kernel (opt-in until it has passed its parity tests on hardware)
-                out = torch.empty((4, s, 40 * d), dtype=torch.int8, device=dev)
-                q4 = q.view(4, 40, s, d).transpose(1, 2).contiguous()      # [B, S, H*D] rows, heads side by side
-                k4 = k.view(4, 40, s, d).transpose(1, 2).contiguous()
-                cases[f"S={s}"]["core_fused_ms"] = round(_event_time(lambda: C.attention_prefill(
-                    q4, k4, vt, out, batch=4, heads=40, head_dim=d, tgt_len=s, src_len=s, ld_q=40 * d,
-                    q_batch_stride=s * 40 * d, ld_k=40 * d, k_batch_stride=s * 40 * d, ld_vt=s,
-                    alpha_qk=1.0 / 127 ** 2, alpha_pv=0.01), 10), 4)
+            # ... and as the one fused kernel (scores and probabilities never leave the SM)
+            out = torch.empty((4, s, 40 * d), dtype=torch.int8, device=dev)
+            q4 = q.view(4, 40, s, d).transpose(1, 2).contiguous()      # [B, S, H*D] rows, heads side by side
+            k4 = k.view(4, 40, s, d).transpose(1, 2).contiguous()
+            cases[f"S={s}"]["core_fused_ms"] = round(_event_time(lambda: C.attention_prefill(
+                q4, k4, vt, out, batch=4, heads=40, head_dim=d, tgt_len=s, src_len=s, ld_q=40 * d,
+                q_batch_stride=s * 40 * d, ld_k=40 * d, k_batch_stride=s * 40 * d, ld_vt=s,
+                alpha_qk=1.0 / 127 ** 2, alpha_pv=0.01), 10), 4)
         gbs = self.bytes_per_step / (ms * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None,

@@ -44,3 +44,12 @@ def assert_quant_close(got, want, min_exact=0.999, what=""):
     exact = float((d == 0).double().mean())
     assert int(d.max()) <= 1, f"{what}: max |d| = {int(d.max())}"
     assert exact >= min_exact, f"{what}: only {exact:.5f} of elements identical"
+
+
+def set_fused_attention(model, on):
+    """Switches every attention module of `model` between the one-kernel causal attention and the
+    scores -> softmax_q -> context chain (the two agree except at rounding ties of a probability)."""
+    for m in model.modules():
+        if hasattr(m, "fused_attention"):
+            m.fused_attention = bool(on)
+    return model

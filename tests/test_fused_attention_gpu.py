@@ -1,21 +1,15 @@
 """Parity of the one-kernel causal prefill attention (ti_attention_prefill_s8) with the CPU oracle's
 scores -> softmax -> x127 -> round -> context chain (torch_int/models/opt.py:131-181).
 
-The fused kernel is compiled into the library but has not been run on hardware yet, and nothing calls
-it by default; these tests are therefore opt-in (TI_RUN_UNVALIDATED=1) until a first supervised run on a
-B200 has passed, at which point the switch goes away.  Tolerance: the context may differ by one unit
-where a probability sat on a rounding tie (the row sum is accumulated in another order than torch's)."""
-import os
-
+Tolerance: the context may differ by one unit where a probability sat on a rounding tie (the row sum
+is accumulated in another order than torch's)."""
 import pytest
 import torch
 
-from helpers import rand_s8
+from helpers import rand_s8, set_fused_attention
 from oracle import w8a8 as O
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("TI_RUN_UNVALIDATED") != "1",
-                                 reason="fused prefill attention: first hardware run is opt-in (TI_RUN_UNVALIDATED=1)")]
+pytestmark = pytest.mark.gpu
 
 
 def oracle_attention(q, k, vt, alpha_qk, alpha_pv):
@@ -67,10 +61,8 @@ def test_fused_attention_in_the_model(cuda_ops):
                         max_position_embeddings=512)
     model = random_int8_opt(cfg, seed=5, device="cuda")
     ids = torch.randint(2, 512, (2, 300), generator=torch.Generator().manual_seed(6)).cuda()
-    base = model(ids).logits
-    for layer in model.model.decoder.layers:
-        layer.self_attn.fused_attention = True
-    fused = model(ids).logits
+    base = set_fused_attention(model, False)(ids).logits
+    fused = set_fused_attention(model, True)(ids).logits
     assert cuda_ops.device_status() == 0
     assert float((fused.argmax(-1) == base.argmax(-1)).double().mean()) > 0.99
     assert float((fused - base).abs().max()) <= 0.05 * float(base.abs().max())

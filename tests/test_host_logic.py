@@ -109,7 +109,7 @@ def test_lm_head_logits_helper_on_cpu():
     assert torch.equal(model._logits(hidden), want)
     assert torch.equal(model._logits(hidden.double()), want)          # cast to the table's dtype first
     attn = model.model.decoder.layers[0].self_attn
-    assert attn.fused_attention is False                              # the unvalidated fused kernel is opt-in
+    assert attn.fused_attention is True                               # one-kernel causal attention is the default
 
 
 def test_from_float_matches_the_reference_modules(golden_dir):

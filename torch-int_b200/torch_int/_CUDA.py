@@ -531,7 +531,7 @@ def attention_prefill(q, k_rows, vt, out, *, batch, heads, head_dim, tgt_len, sr
     """Causal prefill attention in one kernel (ti_attention_prefill_s8): int8 views q (query rows, row
     stride ld_q, head h at column h*head_dim), k_rows (key rows) and vt ([batch, heads, head_dim, ld_vt],
     keys contiguous) -> int8 context written into out [batch, tgt_len, heads*head_dim].  Row t sees keys
-    j <= t + (src_len - tgt_len).  Not yet run on hardware: callers opt in explicitly."""
+    j <= t + (src_len - tgt_len)."""
     for t, name in ((q, "q"), (k_rows, "k_rows"), (vt, "vt"), (out, "out")):
         if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.int8):
             raise RuntimeError(f"{name} must be a CUDA int8 tensor")

@@ -86,10 +86,12 @@ class Int8OPTAttention(nn.Module):
         self.local_heads = num_heads // self.tp.size
         self.local_dim = self.local_heads * self.head_dim
         self.attention_weight_scale = 1.0
-        # Run the causal prefill attention as one fused kernel (C.attention_prefill) instead of
-        # scores GEMM -> softmax -> context GEMM.  Off by default: the fused kernel has not been run
-        # on hardware yet; TI_FUSED_ATTENTION=1 or setting the attribute turns it on.
-        self.fused_attention = os.environ.get("TI_FUSED_ATTENTION", "0") == "1"
+        # Causal, padding-free attention with head_dim 64 or 128 runs as one fused kernel
+        # (C.attention_prefill); everything else, and all inputs when this is False
+        # (TI_FUSED_ATTENTION=0), goes through scores GEMM -> softmax_q -> context GEMM.  The two forms
+        # agree except where a probability sits on a rounding tie (the row sum is accumulated in a
+        # different order), which can move a context value by one unit.
+        self.fused_attention = os.environ.get("TI_FUSED_ATTENTION", "1") != "0"
         self.qk_bmm = BMM_S8T_S8N_F32T(1.0)
         self.pv_bmm = BMM_S8T_S8N_S8T(1.0)
         # column-parallel: each rank owns whole heads
@@ -158,7 +160,7 @@ class Int8OPTAttention(nn.Module):
         hl, d, el = self.local_heads, self.head_dim, self.local_dim
         dev = q.device
         if self.fused_attention and mask is None and causal >= 0 and d in (64, 128):
-            # one kernel; scores and probabilities stay on the SM (opt-in: see fused_attention)
+            # one kernel; scores and probabilities stay on the SM
             out = torch.empty((bsz, tgt_len, el), dtype=torch.int8, device=dev)
             return C.attention_prefill(q, k_rows, vt, out, batch=bsz, heads=hl, head_dim=d, tgt_len=tgt_len,
                                        src_len=src_len, ld_q=q_row_stride, q_batch_stride=tgt_len * q_row_stride,
