@@ -98,20 +98,57 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def start_watchdog(seconds, rank):
-    """Ends the process if the benchmark has not finished after `seconds` (a hung collective or a
-    machine problem must not hold the GPUs until an outer limit kills the job)."""
-    def fire():
-        msg = f"bench.py watchdog: not finished after {seconds} s, giving up"
+_T0 = time.time()
+_RANK = int(os.environ.get("RANK", "0"))
+
+
+def progress(msg):
+    """One line on stderr per phase (rank and seconds since start): a run that stops early shows where."""
+    sys.stderr.write(f"[bench rank {_RANK} +{time.time() - _T0:6.1f}s] {msg}\n")
+    sys.stderr.flush()
+
+
+class Watchdog:
+    """Ends the process if a phase has not finished in time (a hung collective or a machine problem must
+    not hold the GPUs until an outer limit kills the job).  Once the prefill measurement exists, rank 0
+    prints that line - with the unfinished leg reported as an error inside it - and every rank exits 0,
+    so a late failure does not lose the measurement."""
+
+    def __init__(self, rank):
+        self.rank = rank
+        self.line = None          # the JSON line as far as it is known (rank 0)
+        self.salvageable = False  # True once the prefill + end-to-end legs are measured (all ranks)
+        self.phase = "start"
+        self.timer = None
+        self.lock = threading.Lock()
+
+    def arm(self, seconds, phase):
+        with self.lock:
+            if self.timer is not None:
+                self.timer.cancel()
+            self.phase = phase
+            self.timer = threading.Timer(seconds, self._fire, args=(seconds, phase))
+            self.timer.daemon = True
+            self.timer.start()
+
+    def disarm(self):
+        with self.lock:
+            if self.timer is not None:
+                self.timer.cancel()
+                self.timer = None
+
+    def _fire(self, seconds, phase):
+        msg = f"bench.py watchdog: phase '{phase}' not finished after {seconds} s, giving up"
         sys.stderr.write(msg + "\n")
         sys.stderr.flush()
-        if rank == 0:
+        if self.salvageable:
+            if self.rank == 0 and self.line is not None:
+                self.line.setdefault("legs_failed", {})[phase] = msg
+                print(json.dumps(self.line), flush=True)
+            os._exit(0)
+        if self.rank == 0:
             print(json.dumps({"error": msg}), flush=True)
         os._exit(3)
-    t = threading.Timer(seconds, fire)
-    t.daemon = True
-    t.start()
-    return t
 
 
 def dist_env():
@@ -119,6 +156,48 @@ def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     return world, rank, local
+
+
+# DRAM traffic per launch of gemm_i8_kernel, from ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
+# captured launch; the summaries under profiles/ give the commands).  Keyed by (M, N, K).
+NCU_GEMM_TRAFFIC_BYTES = {
+    (4096, 12288, 12288): 474.7e6,
+}
+
+
+def gemm_traffic_bytes(m, n, k):
+    return NCU_GEMM_TRAFFIC_BYTES.get((m, n, k))
+
+
+def headline_gemm_sustained(device, peaks, launches=600):
+    """The headline W8A8 GEMM (4096 x 12288 x 12288, int8 out) back to back for `launches` launches with the
+    SM clock sampled meanwhile: the sustained TOP/s under the power cap."""
+    from torch_int import _CUDA as C
+    m, n, k = HG
+    gd = torch.Generator(device=device).manual_seed(11)
+    x = torch.randint(-127, 128, (m, k), generator=gd, dtype=torch.int8, device=device)
+    w = torch.randint(-127, 128, (n, k), generator=gd, dtype=torch.int8, device=device)
+    b = torch.randint(-127, 128, (n,), generator=gd, dtype=torch.int8, device=device)
+    for _ in range(5):
+        C.linear_a8_w8_b8_o8(x, w, b, 1e-4, 0.01)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        C.linear_a8_w8_b8_o8(x, w, b, 1e-4, 0.01)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / launches
+    tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    sustained = 2.0 * peaks["bf16_tflops_sustained"]
+    return {"shape": [m, n, k], "launches": launches, "ms": round(ms, 4), "tops": round(tops, 1),
+            "frac_of_sustained_peak": round(tops / sustained, 4), "sustained_peak": round(sustained, 1),
+            "frac_of_nominal_4500": round(tops / 4500.0, 4), "sm_mhz_median": clocks.get("sm_mhz"),
+            "reasons": clocks.get("reasons"), "traffic": gemm_traffic_bytes(m, n, k),
+            "algorithmic_bytes": float(m * k + n * k + n + m * n)}
 
 
 # ----------------------------------------------------------------------------- GEMM workload
@@ -167,7 +246,8 @@ class GemmWorkload:
         peak = 2.0 * peaks["bf16_tflops"]
         achieved = self.ops_per_step / (ms * 1e-3) / 1e12
         return {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TOP/s",
-                "frac": round(achieved / peak, 4), "traffic": None,
+                "frac": round(achieved / peak, 4), "traffic": gemm_traffic_bytes(*HG),
+                "algorithmic_bytes": float(HG[0] * HG[2] + HG[1] * HG[2] + HG[1] + HG[0] * HG[1]),
                 "peak_source": f"2 x cuBLAS bf16 burst of MEASURED_PEAKS.json ({peaks['source']}): "
                                "kind::i8 issues at twice the kind::f16 rate",
                 "kernel": "gemm_i8_kernel<256, EPI_S8_BIAS_S8, PAIR=true> (256x256 tiles on CTA pairs)",
@@ -194,6 +274,28 @@ OPT_WORKLOADS = {
     "opt13b": ("opt-13b", 4, 512, 128),
     "opt1.3b": ("opt-1.3b", 8, 512, 32),
 }
+# hidden, layers, heads, ffn of the published OPT architectures (vocabulary 50272)
+OPT_DIMS = {"opt-1.3b": (2048, 24, 32, 8192), "opt-13b": (5120, 40, 40, 20480),
+            "opt-30b": (7168, 48, 56, 28672), "opt-175b": (12288, 96, 96, 49152)}
+OPT_VOCAB = 50272
+
+
+def opt_workload_name(arch, batch, seq, world):
+    return f"int8_{arch}_prefill_b{batch}_s{seq}" + (f"_tp{world}" if world > 1 else "")
+
+
+def opt_config_dict(key, world):
+    """`config` of an OPT workload: the same dictionary for this repository's arm and for the CPU arm
+    (it names the workload, not the implementation)."""
+    arch, batch, seq, _ = OPT_WORKLOADS[key]
+    hidden, layers, heads, ffn = OPT_DIMS[arch]
+    return {"workload": opt_workload_name(arch, batch, seq, world), "architecture": arch, "layers": layers,
+            "hidden": hidden, "heads": heads, "ffn": ffn, "vocab": OPT_VOCAB, "batch": batch, "prefill_len": seq,
+            "arithmetic": "int8 x int8 -> int32 GEMM/BMM, fp32 epilogues and residual stream, fp16 embeddings and lm_head",
+            "parallelism": f"tp{world}" if world > 1 else "single GPU",
+            "weights": "random int8 uniform on [-127,127], analytic per-tensor scales x U(0.7,1.3)",
+            "logits": "all positions (fp16 lm_head)",
+            "l2": "per step the layers stream their int8 weights (>> 126 MB L2)"}
 
 
 class OptWorkload:
@@ -213,10 +315,12 @@ class OptWorkload:
         self.arch = arch
         self.cfg = opt_config(arch)
         self.world = world
-        self.name = f"int8_{arch}_prefill_b{self.batch}_s{self.seq}" + (f"_tp{world}" if world > 1 else "")
+        self.name = opt_workload_name(arch, self.batch, self.seq, world)
         tp = TensorParallel.from_world() if world > 1 else TensorParallel.single()
         self.tp = tp
-        self.model = random_int8_opt(self.cfg, seed=1234 + rank, device=device, tp=tp, param_dtype=torch.float16,
+        # ONE model over all ranks: the same seed everywhere, so that the replicated parameters (scales,
+        # LayerNorm, fp32 biases, embeddings) agree; only the sharded int8 weights are drawn per rank
+        self.model = random_int8_opt(self.cfg, seed=1234, device=device, tp=tp, param_dtype=torch.float16,
                                      consistent=False)
         g = torch.Generator().manual_seed(0)
         self.ids_host = torch.randint(0, self.cfg.vocab_size, (self.batch, self.seq), generator=g).pin_memory()
@@ -247,50 +351,55 @@ class OptWorkload:
         return float(self.batch * self.seq)  # tokens per step over the whole job
 
     def config(self, n_gpus):
-        return {"workload": self.name, "architecture": self.arch, "layers": self.cfg.num_hidden_layers,
-                "hidden": self.cfg.hidden_size, "heads": self.cfg.num_attention_heads, "ffn": self.cfg.ffn_dim,
-                "vocab": self.cfg.vocab_size, "batch": self.batch, "prefill_len": self.seq,
-                "arithmetic": self.arithmetic,
-                "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single GPU",
-                "exchange": ("none" if n_gpus == 1 else
-                             (f"peer memory ({self.tp.peer_mode}): partial sums to the owners' slabs -> barrier -> "
-                              "reduce+LayerNorm kernel with peer stores -> barrier")
-                             if (self.tp.use_peer_memory and self.tp._workspaces) else
-                             "NCCL reduce-scatter / all-gather on a communication stream"),
-                "weights": "random int8 uniform on [-127,127], analytic per-tensor scales x U(0.7,1.3)",
-                "logits": "all positions (fp16 lm_head)",
-                "l2": "per step the layers stream their int8 weights (>> 126 MB L2)"}
+        return opt_config_dict(self.key, n_gpus)
+
+    def exchange(self):
+        """How the two per-layer exchanges of the tensor-parallel run were carried out."""
+        if self.world == 1:
+            return "none"
+        if self.tp.use_peer_memory and self.tp._workspaces:
+            return (f"peer memory ({self.tp.peer_mode}): partial sums to the owners' slabs -> barrier -> "
+                    "reduce+LayerNorm kernel with peer stores -> barrier")
+        return "NCCL reduce-scatter / all-gather on a communication stream"
+
+    def ranks_agree(self):
+        """True when every rank's greedy next tokens of the last end-to-end step are the same (they must
+        be: all ranks hold one model and finish with the same logits)."""
+        import torch.distributed as dist
+        mine = self.next_host.to(self.device)
+        allv = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(allv, mine)
+        return all(bool(torch.equal(allv[0], v)) for v in allv)
 
     def roofline(self, ms, peaks):
-        """The dominant kernel is the W8A8 GEMM: time the layer's largest one (fc1) alone, live."""
-        e, f = self.cfg.hidden_size, self.cfg.ffn_dim
+        """The dominant kernel is the W8A8 GEMM: the layer's largest one (fc1) is timed alone, live, in a
+        burst of back-to-back launches, so the denominator is the burst figure (2 x cuBLAS bf16 burst);
+        the whole step is held against the sustained figure beside it."""
+        e = self.cfg.hidden_size
         t = self.batch * self.seq
         layer = self.model.model.decoder.layers[0]
         x = torch.randint(-127, 128, (t, e), dtype=torch.int8, device=self.device)
-        fn = lambda: layer.fc1._op(x)
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 20
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        gms = e0.elapsed_time(e1) / reps
-        ops = 2.0 * t * layer.local_ffn * e
+        gms = _event_time(lambda: layer.fc1._op(x), 20)
+        n = layer.local_ffn
+        ops = 2.0 * t * n * e
         achieved = ops / (gms * 1e-3) / 1e12
-        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        peak = 2.0 * peaks["bf16_tflops"]
+        sustained = 2.0 * peaks["bf16_tflops_sustained"]
         step_ops = (self.gemm_ops + self.bmm_ops) / self.world
-        return {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TOP/s",
-                "frac": round(achieved / peak, 4), "traffic": None,
-                "kernel": f"gemm_i8_kernel (fc1: {t} x {layer.local_ffn} x {e}, ReLU int8 epilogue)",
-                "kernel_ms": round(gms, 4),
-                "peak_source": f"2 x cuBLAS bf16 sustained of MEASURED_PEAKS.json ({peaks['source']}); "
-                               "sustained because the kernel runs inside a long step",
-                "step_int8_tops_per_gpu": round(step_ops / (ms * 1e-3) / 1e12, 1),
-                "step_frac_of_peak": round(step_ops / (ms * 1e-3) / 1e12 / peak, 4)}
+        algorithmic = float(t * e + n * e + n + t * n)
+        out = {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TOP/s",
+               "frac": round(achieved / peak, 4),
+               "traffic": gemm_traffic_bytes(t, n, e), "algorithmic_bytes": algorithmic,
+               "kernel": f"gemm_i8_kernel (fc1: {t} x {n} x {e}, ReLU int8 epilogue)",
+               "kernel_ms": round(gms, 4),
+               "peak_source": f"2 x cuBLAS bf16 burst of MEASURED_PEAKS.json ({peaks['source']}): the kernel is timed "
+                              "alone in a 20-launch burst; kind::i8 issues at twice the kind::f16 rate",
+               "step_int8_tops_per_gpu": round(step_ops / (ms * 1e-3) / 1e12, 1),
+               "step_frac_of_sustained_peak": round(step_ops / (ms * 1e-3) / 1e12 / sustained, 4),
+               "sustained_peak": round(sustained, 1)}
+        if self.world == 1:
+            out["headline_gemm"] = headline_gemm_sustained(self.device, peaks)
+        return out
 
     def decode_rate(self, steps=None):
         """Greedy decoding with the static int8 cache after the prefill: tokens/s over `steps` one-token
@@ -333,27 +442,61 @@ class OptWorkload:
         return opt_cpu_sample(self.arch, self.batch, self.seq)
 
 
-def opt_cpu_sample(arch, batch, seq, tokens=64):
-    """Bounded CPU sample: ONE decoder layer at the full dimensions of `arch` on `tokens`
-    tokens of one sequence, evaluated by the oracle; the rate is extrapolated to the
-    whole model as tokens / (layer time x layers) and labelled as such."""
+def reference_layer_state(arch, seed=5):
+    """State dict (the reference's buffer names) of ONE random Int8 OPT decoder layer at the dimensions
+    of `arch`, built with torch alone: the CPU arm must not load this repository's package or library.
+    Weights uniform int8; scales chosen so that int8 activations keep a standard deviation of a few tens."""
+    import math
+    h, _, heads, ffn = OPT_DIMS[arch]
+    g = torch.Generator().manual_seed(seed)
+    sw, sa = 127.0 / math.sqrt(3.0), 30.0
+    pre = "model.decoder.layers.0"
+    sd = {}
+
+    def s8(*shape):
+        return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8)
+
+    for name in ("q_proj", "k_proj", "v_proj"):
+        sd[f"{pre}.self_attn.{name}.weight"] = s8(h, h)
+        sd[f"{pre}.self_attn.{name}.bias"] = s8(1, h)
+        sd[f"{pre}.self_attn.{name}.a"] = torch.tensor(sa / (sa * sw * math.sqrt(h)))
+        sd[f"{pre}.self_attn.{name}.b"] = torch.tensor(0.05)
+    sd[f"{pre}.self_attn.qk_bmm.a"] = torch.tensor(1.5 / (sa * sa * math.sqrt(h // heads)))
+    sd[f"{pre}.self_attn.pv_bmm.a"] = torch.tensor(0.05)
+    sd[f"{pre}.self_attn.out_proj.weight"] = s8(h, h)
+    sd[f"{pre}.self_attn.out_proj.bias"] = torch.randn((1, h), generator=g) * 0.02
+    sd[f"{pre}.self_attn.out_proj.a"] = torch.tensor(0.3 / (10.0 * sw * math.sqrt(h)))
+    sd[f"{pre}.fc1.weight"] = s8(ffn, h)
+    sd[f"{pre}.fc1.bias"] = s8(1, ffn)
+    sd[f"{pre}.fc1.a"] = torch.tensor(40.0 / (sa * sw * math.sqrt(h)))
+    sd[f"{pre}.fc1.b"] = torch.tensor(0.05)
+    sd[f"{pre}.fc2.weight"] = s8(h, ffn)
+    sd[f"{pre}.fc2.bias"] = torch.randn((1, h), generator=g) * 0.02
+    sd[f"{pre}.fc2.a"] = torch.tensor(0.3 / (25.0 * sw * math.sqrt(ffn)))
+    for ln in ("self_attn_layer_norm", "final_layer_norm"):
+        sd[f"{pre}.{ln}.weight"] = torch.randn(h, generator=g) * (0.1 * sa) + sa
+        sd[f"{pre}.{ln}.bias"] = torch.randn(h, generator=g) * (0.1 * sa)
+    return sd, pre, heads
+
+
+def opt_cpu_sample(arch, batch, seq, tokens=None):
+    """Bounded CPU sample: ONE decoder layer at the full dimensions of `arch` on one whole sequence
+    (`tokens` = min(seq, 512) tokens, so the host is compute bound rather than streaming the layer's
+    weights for a few rows), evaluated by the oracle; the rate is extrapolated to the whole model as
+    tokens / (layer time x layers) and labelled as such."""
     from oracle import opt_model as OM
     from oracle import w8a8 as O
-    from torch_int.models.opt import Int8OPTConfig
-    from torch_int.models.random_init import OPT_ARCHS, random_int8_opt
-    h, layers, heads, ffn = OPT_ARCHS[arch]
-    cfg = Int8OPTConfig(vocab_size=64, hidden_size=h, num_hidden_layers=1, ffn_dim=ffn, num_attention_heads=heads,
-                        max_position_embeddings=tokens + 2)
-    model = random_int8_opt(cfg, seed=5, device="cpu", consistent=False)
-    sd = {k: v.detach() for k, v in model.state_dict().items()}
+    tokens = tokens or min(seq, 512)
+    layers = OPT_DIMS[arch][1]
+    sd, prefix, heads = reference_layer_state(arch)
     g = torch.Generator().manual_seed(1)
-    hidden = torch.randn((1, tokens, h), generator=g)
+    hidden = torch.randn((1, tokens, OPT_DIMS[arch][0]), generator=g)
     mask = O.causal_mask(1, tokens, tokens)
 
     def run():
-        return OM.decoder_layer(sd, "model.decoder.layers.0", hidden, mask, heads)
+        return OM.decoder_layer(sd, prefix, hidden, mask, heads)
     units = tokens / float(layers)  # tokens per (layer-time x layers)
-    return run, units, (f"one {arch} decoder layer at full dimensions on {tokens} tokens of one sequence, "
+    return run, units, (f"one {arch} decoder layer at full dimensions on one {tokens}-token sequence, "
                         f"extrapolated x{layers} layers (embeddings and lm_head not included)"), O.num_threads()
 
 
@@ -590,7 +733,8 @@ def pick_workload(name, world):
 
 def run_reference(args, world, rank):
     """CPU arm: the reference semantics on the host cores (the oracle's C port; the reference
-    itself has no CPU implementation of its GEMM/BMM path and cannot be built without CUTLASS)."""
+    itself has no CPU implementation of its GEMM/BMM path and cannot be built without CUTLASS).
+    Loads neither this repository's package nor its CUDA library."""
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
@@ -605,20 +749,27 @@ def run_reference(args, world, rank):
         wl.b = torch.randint(-127, 128, (n,), generator=g1, dtype=torch.int8)
         wl.alpha, wl.beta = 1e-4, 0.01
         run, units, sample, cores = wl.cpu_sample()
-        metric, unit, dtype, scaling, name = (GemmWorkload.metric, GemmWorkload.unit, GemmWorkload.dtype,
-                                              GemmWorkload.scaling, GemmWorkload.name)
-        config = {"workload": name, "M": HG[0], "N": HG[1], "K": HG[2], "sample": sample}
+        metric, unit, dtype, scaling = GemmWorkload.metric, GemmWorkload.unit, GemmWorkload.dtype, GemmWorkload.scaling
+        config = GemmWorkload.config(wl, world)
     elif key in ("norm", "bmm"):
         WL = RowKernelWorkload if key == "norm" else BmmWorkload
         run, units, sample, cores = WL.cpu_sample(None)
-        metric, unit, dtype, scaling, name = WL.metric, WL.unit, WL.dtype, WL.scaling, WL.name
-        config = {"workload": name, "sample": sample}
+        metric, unit, dtype, scaling = WL.metric, WL.unit, WL.dtype, WL.scaling
+        config = WL.config(WL.__new__(WL), world)
     else:
         arch, batch, seq, _ = OPT_WORKLOADS[key]
-        run, units, sample, cores = opt_cpu_sample(arch, batch, seq)
+        tokens = min(seq, 512)
+        while True:
+            run, units, sample, cores = opt_cpu_sample(arch, batch, seq, tokens)
+            t0 = time.perf_counter()
+            run()
+            first = time.perf_counter() - t0
+            # keep the whole --steps/--warmup run within a few minutes: halve the sample if it would not fit
+            if first * (min(args.steps, 20) + 2) <= 240.0 or tokens <= 64:
+                break
+            tokens //= 2
         metric, unit, dtype, scaling = OptWorkload.metric, OptWorkload.unit, OptWorkload.dtype, OptWorkload.scaling
-        name = f"int8_{arch}_prefill_b{batch}_s{seq}" + (f"_tp{world}" if world > 1 else "")
-        config = {"workload": name, "architecture": arch, "batch": batch, "prefill_len": seq, "sample": sample}
+        config = opt_config_dict(key, world)
     for _ in range(max(1, min(args.warmup, 2))):
         run()
     steps = max(1, min(args.steps, 20))
@@ -666,13 +817,19 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
-    start_watchdog(int(os.environ.get("TI_BENCH_DEADLINE_S", "600")), rank)
+    dog = Watchdog(rank)
+    deadline = int(os.environ.get("TI_BENCH_DEADLINE_S", "600"))
+    dog.arm(deadline, "setup and prefill measurement")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
         import datetime
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
+        # a collective that does not finish within this limit aborts the rank: well below the
+        # deadline above, so that a hang is reported by the rank that saw it
+        dist.init_process_group("nccl", device_id=device,
+                                timeout=datetime.timedelta(seconds=int(os.environ.get("TI_BENCH_NCCL_TIMEOUT_S", "120"))))
+        progress("process group initialised")
     if key == "gemm":
         wl = GemmWorkload(device)
     elif key == "norm":
@@ -681,36 +838,78 @@ def main():
         wl = BmmWorkload(device)
     else:
         wl = OptWorkload(device, key, world, rank)
+    progress(f"workload {key} built, first step done")
     peaks = measured_peaks()
     from torch_int import _CUDA as C
 
-    def agreed_status():
-        """Kernel status word, maximum over the ranks (every rank takes the same decision)."""
-        st = C.device_status(reset=True)
+    def agreed_max(value):
+        """Maximum of an integer over the ranks: every rank then takes the same decision."""
         if world > 1:
             import torch.distributed as dist
-            t = torch.tensor([st], dtype=torch.int32, device=device)
+            t = torch.tensor([int(value)], dtype=torch.int32, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            st = int(t.item())
-        return st
+            value = int(t.item())
+        return int(value)
 
-    if key in OPT_WORKLOADS and world > 1 and agreed_status() != 0 and wl.tp.use_peer_memory:
-        # the first step (run while the workload was built) hit a bounded-wait time limit in the
-        # peer-memory exchange: use NCCL collectives for the measurement instead
-        wl.tp.use_peer_memory = False
-        wl.step()
-        assert agreed_status() == 0, "a kernel reported a wait timeout"
+    def agreed_status():
+        return agreed_max(C.device_status(reset=True))
+
+    if key in OPT_WORKLOADS and world > 1:
+        st = agreed_status()
+        peer = agreed_max(1 if wl.tp.use_peer_memory else 0)   # a per-rank flag: agree on it before branching
+        if st != 0 and peer:
+            # the first step (run while the workload was built) hit a bounded-wait time limit in the
+            # peer-memory exchange: all ranks use NCCL collectives for the measurement instead
+            progress(f"first step reported status {st}: switching every rank to the NCCL exchange")
+            wl.tp.use_peer_memory = False
+            wl.step()
+            st = agreed_status()
+        assert st == 0, f"a kernel reported wait timeout {st}"
 
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
     ms = time_steps(wl.step, args.steps, args.warmup, world)
     clocks = sampler.stop() if sampler else None
+    progress(f"prefill timed: {ms:.3f} ms/step")
     ms_e2e = ms if args.profile else time_steps(wl.step_e2e, args.steps, args.warmup, world)
+    progress(f"end-to-end timed: {ms_e2e:.3f} ms/step")
+    status = agreed_status()
+    assert status == 0, f"a kernel reported wait timeout {status}"
+    agree = None
+    if key in OPT_WORKLOADS and world > 1 and not args.profile:
+        agree = bool(agreed_max(0 if wl.ranks_agree() else 1) == 0)
+    line = None
+    if rank == 0:
+        units = wl.units(world)
+        line = {"metric": wl.metric, "value": round(units / (ms * 1e-3), 2), "unit": wl.unit, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+                "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
+                "data": "synthetic (seeded random int8 weights and inputs)", "config": wl.config(world),
+                "e2e": {"value": round(units / (ms_e2e * 1e-3), 2), "unit": wl.unit,
+                        "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                        "ms_per_step": round(ms_e2e, 4)},
+                "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
+        if key in OPT_WORKLOADS:
+            line["tp_exchange"] = wl.exchange()
+        if agree is not None:
+            line["tp_ranks_agree"] = agree
+    # From here on a failure must not lose the measurement: the watchdog prints `line` as it stands.
+    dog.line, dog.salvageable = line, True
+    leg_deadline = int(os.environ.get("TI_BENCH_LEG_DEADLINE_S", "100"))
     extra = {}
     if key in OPT_WORKLOADS and not args.profile and not args.no_decode:
-        extra = wl.decode_rate()
+        dog.arm(leg_deadline, "decode")
+        try:
+            extra.update(wl.decode_rate())
+            st = agreed_status()
+            if st != 0:
+                extra["decode_error"] = f"a kernel reported wait timeout {st}"
+        except Exception as exc:  # noqa: BLE001 - reported in the line; the prefill measurement stands
+            extra["decode_error"] = f"{type(exc).__name__}: {exc}"
+        progress("decode leg done")
     if args.trace and key in OPT_WORKLOADS and world > 1:
+        dog.arm(leg_deadline, "trace")
         from torch_int.models.tensor_parallel import StreamTrace
         wl.tp.trace = StreamTrace()
         wl.step()
@@ -722,26 +921,22 @@ def main():
                                    "extent_ms": round((v["last_us"] - v["first_us"]) / 1e3, 2),
                                    "by_name_ms": {k: round(t / 1e3, 2) for k, t in v["by_name"].items()}}
                              for row, v in trace.summary().items()}
-    status = agreed_status()
-    assert status == 0, f"a kernel reported wait timeout {status}"
+        progress("trace leg done")
     if rank == 0:
-        units = wl.units(world)
-        line = {"metric": wl.metric, "value": round(units / (ms * 1e-3), 2), "unit": wl.unit, "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
-                "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
-                "data": "synthetic (seeded random int8 weights and inputs)", "config": wl.config(world),
-                "e2e": {"value": round(units / (ms_e2e * 1e-3), 2), "unit": wl.unit,
-                        "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                        "ms_per_step": round(ms_e2e, 4)},
-                "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks,
-                "roofline": wl.roofline(ms, peaks)}
+        dog.arm(leg_deadline + 60, "roofline and CPU baseline")
+        line.update(extra)
+        line["roofline"] = wl.roofline(ms, peaks)
         if world == 1 and not args.no_cpu_baseline and not args.profile:
             line["cpu_baseline"] = cpu_baseline(wl)
-        line.update(extra)
+        dog.disarm()
         print(json.dumps(line), flush=True)
+    dog.disarm()
+    progress("line printed" if rank == 0 else "done")
     if world > 1:
         import torch.distributed as dist
+        dog.arm(60, "teardown")
         dist.destroy_process_group()
+        dog.disarm()
 
 
 if __name__ == "__main__":

@@ -31,7 +31,7 @@ extern "C" {
 #define TI_OK 0
 #define TI_E_INVALID (-1) /* bad shape, alignment or pointer */
 #define TI_E_CUDA (-2)    /* a CUDA runtime / driver call failed */
-#define TI_E_DEVICE (-3)  /* a kernel's bounded wait gave up (see ti_device_status) */
+#define TI_E_DEVICE (-3)  /* returned by ti_check_device: a kernel's bounded wait gave up */
 
 /* ---- linear layers: out[M,N] = epilogue(input[M,K] . weight[N,K]^T, bias[N]) ---- */
 
@@ -72,7 +72,9 @@ int ti_linear_a8_w8_b32_o32_with_scaling(const int8_t* input, const int8_t* weig
  * by any library this calls.  Refused with an error: M > 128, or ti_split_k_workspace_bytes(M, N) >
  * 4 MiB (e.g. M = 16 allows N up to 65024).  The array is shared by all calls and keeps the last
  * call's contents: the kernel re-zeroes what it used, so back-to-back calls on one stream are fine, but
- * calls that overlap on the GPU race on it - serialise them.  The first call on each device resolves
+ * calls that overlap on the GPU race on it - serialise them.  If a launch gave up on a bounded wait
+ * (ti_device_status reports non-zero) the array may be left non-zero: ti_device_status(reset != 0)
+ * clears it together with the status word.  The first call on each device resolves
  * the array's device address (cudaGetSymbolAddress, with that device current); make that first call
  * before starting any stream capture.
  * No counterpart in the reference, which allocates a fresh output and workspace in every call
@@ -233,8 +235,7 @@ int ti_advance_position(int32_t* position, int32_t by, void* stream);
  * strides multiples of 16.  No additive mask: callers with padding masks use ti_gemm_i8_ex + ti_softmax_q.
  * Replaces bmm_s8t_s8n_f32t -> mask/softmax/x127/round -> bmm_s8t_s8n_s8t of Int8OPTAttention.forward
  * (torch_int/models/opt.py:131-181).  Rounding: the row sum is accumulated tile by tile, so p may differ
- * from the three-kernel path by one unit on rounding ties.
- * STATUS: compiled for sm_100a but not yet run on hardware; nothing in the library calls it by default. */
+ * from the three-kernel path by one unit on rounding ties. */
 int ti_attention_prefill_s8(const int8_t* q, int64_t ld_q, int64_t q_batch_stride, const int8_t* k, int64_t ld_k,
                             int64_t k_batch_stride, const int8_t* vt, int64_t ld_vt, int8_t* ctx, int64_t ld_ctx,
                             int64_t ctx_batch_stride, int64_t batch, int64_t heads, int64_t head_dim, int64_t T,
@@ -247,8 +248,16 @@ const char* ti_last_error(void);
 
 /* Synchronises the current device and stores the kernel status word in *status:
  * 0 = ok, else the code of the first in-kernel wait that ran into its time
- * limit (the kernels never spin forever).  reset != 0 clears it. */
+ * limit (the kernels never spin forever).  reset != 0 clears it and, when it was
+ * non-zero, also zeroes the built-in split-K scratch of ti_linear_a8_w8_b8_o8_static
+ * (a launch that gave up may have left partial sums there).  A workspace the caller
+ * passed through ti_gemm_desc.workspace must be zeroed by the caller in that case.
+ * Returns TI_OK when the word could be read (whatever its value), TI_E_CUDA otherwise. */
 int ti_device_status(int* status, int reset);
+
+/* ti_device_status(&s, reset) as a plain check: TI_OK when the status word was 0, TI_E_DEVICE (with the
+ * code in ti_last_error()) when a kernel's bounded wait had given up, TI_E_CUDA on a runtime error. */
+int ti_check_device(int reset);
 
 /* ---- tensor-parallel exchange (no reference counterpart: the reference is single-GPU) ---- */
 
@@ -262,11 +271,34 @@ int ti_tp_reduce_layernorm_q(const int32_t* stage, int32_t n_partials, int64_t p
                              const float* beta, float eps, float* residual_out, void* const* q_dst,
                              int32_t n_dst, int64_t q_row_offset, int64_t rows, int64_t H, void* stream);
 
+/* ti_tp_reduce_layernorm_q with the synchronisation of the exchange folded in, so that one exchange is
+ * "copy the partial sums into the owners' stage slabs, then this one kernel".  The kernel (1) tells every
+ * rank that this rank's partial sums have arrived (the copies precede it in stream order), (2) waits
+ * until all ranks have said so, (3) reduces, normalises and stores the int8 rows into every rank's
+ * buffer, and (4) its last CTA tells every rank that this rank is complete and waits for the same from
+ * all ranks: when the kernel ends, every rank's rows are in this rank's buffer and every stage may be
+ * overwritten.  pads[i] = rank i's pad of 16 zero-initialised 32-bit words in peer-accessible memory
+ * (words [0, 8): arrival, [8, 16): completion); epoch must increase by one per call on every rank;
+ * counter = one zero-initialised int32 in this GPU's memory, used by this call only while it runs.
+ * Waits are bounded by limit_ms (<= 0: 2000; at most 60000); on expiry the status word of
+ * ti_device_status is set to 105, no later wait of the process blocks, and the output of that pass is
+ * invalid.  No reference counterpart (the reference is single-GPU). */
+int ti_tp_exchange_reduce_layernorm_q(const int32_t* stage, int32_t n_partials, int64_t partial_stride,
+                                      float scale, const float* bias, const float* residual, const float* gamma,
+                                      const float* beta, float eps, float* residual_out, void* const* q_dst,
+                                      int32_t n_dst, int64_t q_row_offset, int64_t rows, int64_t H,
+                                      void* const* pads, int32_t rank, int32_t n, uint32_t epoch,
+                                      int32_t* counter, int64_t limit_ms, void* stream);
+
 /* Stream-ordered barrier over n <= 8 ranks.  pads[i] = rank i's pad (n 32-bit words, zeroed once,
  * peer-accessible); epoch must increase by one per call on every rank.  Peer stores made by earlier
  * work of `stream` are visible to the peers' work enqueued after their matching barrier.  The wait is
  * bounded (2 s); on expiry the status word of ti_device_status is set to 105. */
 int ti_tp_barrier(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, void* stream);
+/* The same with the time limit of the wait given in milliseconds (<= 0: 2000; at most 60000): the first
+ * barriers of a process tolerate the seconds by which ranks may reach them apart while kernels load. */
+int ti_tp_barrier_limit(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, int64_t limit_ms,
+                        void* stream);
 
 /* Caps the number of SMs the persistent GEMM/BMM grids of this process occupy (0 = all).  For callers
  * that run collectives concurrently with the GEMMs and want the collective's CTAs to find free SMs.

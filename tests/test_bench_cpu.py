@@ -27,6 +27,24 @@ def test_reference_arm_prints_one_json_line(workload, metric):
     assert "workload" in d["config"]
 
 
+def test_reference_arm_does_not_load_the_product():
+    """The CPU arm must map neither the product package nor its CUDA library, and its `config` is the one
+    the repository's own arm reports for the same workload."""
+    code = ("import runpy, sys, json, io, contextlib\n"
+            "sys.argv = ['bench.py', '--impl', 'reference', '--workload', 'opt1.3b', '--steps', '1', '--warmup', '1']\n"
+            "buf = io.StringIO()\n"
+            "with contextlib.redirect_stdout(buf):\n"
+            "    mod = runpy.run_path('bench.py', run_name='__main__')\n"
+            "assert not any(m == 'torch_int' or m.startswith('torch_int.') for m in sys.modules), 'product imported'\n"
+            "maps = open('/proc/self/maps').read()\n"
+            "assert 'libtorch_int_b200' not in maps, 'product library mapped'\n"
+            "line = json.loads(buf.getvalue().strip())\n"
+            "assert line['config'] == mod['opt_config_dict']('opt1.3b', 1), line['config']\n"
+            "assert '512-token sequence' in line['cpu_baseline']['sample']\n")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+
+
 def test_reference_arm_other_ranks_do_nothing():
     env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],

@@ -211,3 +211,93 @@ def test_product_model_on_cpu_ranks(world):
         assert pr.exitcode == 0, f"rank exited with {pr.exitcode}"
     for r in range(world):
         assert all(ret[r].values()), f"rank {r}: {ret[r]}"
+
+
+# --------------------------------------------------------------- collective decisions of the exchange
+def _decision_rank_main(rank, world, port, ret):
+    """Host logic that decides between the peer-memory exchange and NCCL: a failure seen by ONE rank
+    (allocation, or a barrier whose wait ran out) must move ALL ranks, at the same point."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import cpu_ops_stub as stub
+        import torch_int.models.tensor_parallel as tpm
+        from torch_int.models.tensor_parallel import PeerWorkspace, TensorParallel
+        checks = {}
+        # 1. the allocation fails on rank 1 only: every rank gets None and switches to NCCL together
+        tp = TensorParallel.from_world()
+        calls = []
+
+        def allocate(self, tp_, chunks, mc, e, device):
+            calls.append("allocate")
+            if tp_.rank == 1:
+                raise RuntimeError("out of symmetric memory (injected)")
+            self.tp = tp_
+
+        def preflight(self):
+            calls.append("preflight")
+
+        PeerWorkspace._allocate, PeerWorkspace._map_and_preflight = allocate, preflight
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            ws = tp.peer_workspace(2, 64, 32, "cpu")
+        checks["all_fall_back"] = ws is None and tp.use_peer_memory is False
+        checks["no_rank_went_on_alone"] = "preflight" not in calls     # nobody entered the next collective phase
+        # 2. the preflight fails on the last rank only
+        tp = TensorParallel.from_world()
+        calls.clear()
+
+        def allocate_ok(self, tp_, chunks, mc, e, device):
+            self.tp = tp_
+
+        def preflight_bad(self):
+            if self.tp.rank == world - 1:
+                raise RuntimeError("peer-memory barrier preflight failed (injected)")
+
+        PeerWorkspace._allocate, PeerWorkspace._map_and_preflight = allocate_ok, preflight_bad
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            checks["preflight_failure_is_collective"] = tp.peer_workspace(2, 64, 32, "cpu") is None and not tp.use_peer_memory
+        # 3. everything fine: all ranks get a workspace, cached under its key
+        tp = TensorParallel.from_world()
+        PeerWorkspace._map_and_preflight = lambda self: None
+        ws = tp.peer_workspace(2, 64, 32, "cpu")
+        checks["workspace"] = ws is not None and tp.peer_workspace(2, 64, 32, "cpu") is ws and ws.checked is False
+        # 4. after a pass, rank 0 alone finds status 105: all ranks raise, drop the workspace, use NCCL next
+        stub.device_status = lambda reset=False: 105 if rank == 0 else 0
+        import torch_int
+        torch_int._CUDA = stub                       # check_exchange imports the module lazily
+        import sys
+        sys.modules["torch_int._CUDA"] = stub
+        raised = False
+        try:
+            tp.check_exchange(ws, "cpu")
+        except RuntimeError as exc:
+            raised = "status 105" in str(exc)
+        checks["status_is_agreed"] = raised and tp.use_peer_memory is False and not tp._workspaces and ws.checked
+        # 5. a clean status marks the workspace as checked and keeps the peer path
+        tp = TensorParallel.from_world()
+        ws = tp.peer_workspace(2, 64, 32, "cpu")
+        stub.device_status = lambda reset=False: 0
+        tp.check_exchange(ws, "cpu")
+        checks["clean_pass"] = ws.checked and tp.use_peer_memory and tp.peer_workspace(2, 64, 32, "cpu") is ws
+        ret[rank] = checks
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_or_nccl_is_decided_by_all_ranks_together(world):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_decision_rank_main, args=(r, world, port, ret)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=120)
+        assert pr.exitcode == 0, f"rank exited with {pr.exitcode}"
+    for r in range(world):
+        assert all(ret[r].values()), f"rank {r}: {ret[r]}"

@@ -243,22 +243,61 @@ int ti_device_status(int* status, int reset) {
   return device_status(status, reset != 0);
 }
 
+int ti_check_device(int reset) {
+  int v = 0;
+  const int rc = device_status(&v, reset != 0);
+  if (rc != TI_OK) return rc;
+  if (v != 0) {
+    set_error("a kernel's bounded wait gave up (status %d)", v);
+    return TI_E_DEVICE;
+  }
+  return TI_OK;
+}
+
 int ti_tp_reduce_layernorm_q(const int32_t* stage, int32_t n_partials, int64_t partial_stride,
                              float scale, const float* bias, const float* residual, const float* gamma,
                              const float* beta, float eps, float* residual_out, void* const* q_dst,
                              int32_t n_dst, int64_t q_row_offset, int64_t rows, int64_t H, void* stream) {
   return tp_reduce_layernorm_q(stage, n_partials, partial_stride, scale, bias, residual, gamma, beta, eps,
-                               residual_out, q_dst, n_dst, q_row_offset, rows, H,
+                               residual_out, q_dst, n_dst, q_row_offset, rows, H, nullptr,
                                static_cast<cudaStream_t>(stream));
 }
 
-int ti_tp_barrier(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, void* stream) {
+int ti_tp_exchange_reduce_layernorm_q(const int32_t* stage, int32_t n_partials, int64_t partial_stride,
+                                      float scale, const float* bias, const float* residual, const float* gamma,
+                                      const float* beta, float eps, float* residual_out, void* const* q_dst,
+                                      int32_t n_dst, int64_t q_row_offset, int64_t rows, int64_t H,
+                                      void* const* pads, int32_t rank, int32_t n, uint32_t epoch,
+                                      int32_t* counter, int64_t limit_ms, void* stream) {
+  TpSync sync;
+  sync.pads = pads;
+  sync.rank = rank;
+  sync.n = n;
+  sync.epoch = epoch;
+  sync.counter = counter;
+  sync.status = status_word_ptr();
+  sync.limit_ms = limit_ms;
+  if (sync.status == nullptr) {
+    set_error("ti_tp_exchange_reduce_layernorm_q: cannot resolve the device status word");
+    return TI_E_CUDA;
+  }
+  return tp_reduce_layernorm_q(stage, n_partials, partial_stride, scale, bias, residual, gamma, beta, eps,
+                               residual_out, q_dst, n_dst, q_row_offset, rows, H, &sync,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int ti_tp_barrier_limit(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, int64_t limit_ms,
+                        void* stream) {
   int* status = status_word_ptr();
   if (status == nullptr) {
     set_error("ti_tp_barrier: cannot resolve the device status word");
     return TI_E_CUDA;
   }
-  return tp_barrier(pads, rank, n, epoch, status, static_cast<cudaStream_t>(stream));
+  return tp_barrier(pads, rank, n, epoch, status, limit_ms, static_cast<cudaStream_t>(stream));
+}
+
+int ti_tp_barrier(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, void* stream) {
+  return ti_tp_barrier_limit(pads, rank, n, epoch, 2000, stream);
 }
 
 int64_t ti_split_k_workspace_bytes(int64_t M, int64_t N) { return split_k_workspace_bytes(M, N); }

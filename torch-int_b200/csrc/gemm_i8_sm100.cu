@@ -927,45 +927,6 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
   return TI_E_INVALID;
 }
 
-// Device address of the status word, for kernels of other translation units.
-int* status_word_ptr() {
-  static int* cached[64] = {nullptr};  // resolved once per device (not during stream capture)
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (cached[dev] == nullptr) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, ti_kernel_status) != cudaSuccess) return nullptr;
-    cached[dev] = static_cast<int*>(p);
-  }
-  return cached[dev];
-}
-
-int64_t split_k_workspace_bytes(int64_t M, int64_t N) { return counter_bytes(32, N) + M * N * 4; }
-
-void set_sm_limit(int sms) { g_sm_limit = sms > 0 ? sms : 0; }
-
-// Reads (and optionally clears) the status word the kernels of this file set
-// when a bounded wait gives up.  Synchronises the device.
-int device_status(int* status, bool reset) {
-  cudaError_t e = cudaDeviceSynchronize();
-  if (e != cudaSuccess) {
-    set_error("cudaDeviceSynchronize failed: %s", cudaGetErrorString(e));
-    return TI_E_CUDA;
-  }
-  int v = 0;
-  e = cudaMemcpyFromSymbol(&v, ti_kernel_status, sizeof(int));
-  if (e != cudaSuccess) {
-    set_error("cudaMemcpyFromSymbol failed: %s", cudaGetErrorString(e));
-    return TI_E_CUDA;
-  }
-  if (reset && v != 0) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(ti_kernel_status, &zero, sizeof(int));
-  }
-  *status = v;
-  return TI_OK;
-}
-
 // ------------------------------------------------- entry point that allocates nothing
 //
 // ti_linear_a8_w8_b8_o8_static: the int8-output linear for few rows (decode steps) with its
@@ -986,6 +947,9 @@ int device_status(int* status, bool reset) {
 //   * the array keeps whatever the last call left in it.  The split-K kernel needs it all zero
 //     on entry and restores every word it touched to zero before it ends, and the array starts
 //     zeroed when the library is loaded, so consecutive calls on one stream are safe;
+//   * the one exception: a launch whose bounded wait gave up (ti_device_status reports non-zero)
+//     may leave partial sums and counters behind.  ti_device_status(reset != 0) clears the array
+//     together with the status word; until then results of this entry point are not trustworthy;
 //   * two calls that overlap on the GPU (different streams, or different host threads feeding
 //     different streams) would add into the same words: do not do that - serialise them;
 //   * the array's name is only a host-side handle; the device address is looked up with
@@ -1022,6 +986,56 @@ int static_scratch_address(void** out) {
   return TI_OK;
 }
 }  // namespace
+
+// Device address of the status word, for kernels of other translation units.
+int* status_word_ptr() {
+  static int* cached[64] = {nullptr};  // resolved once per device (not during stream capture)
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, ti_kernel_status) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
+}
+
+int64_t split_k_workspace_bytes(int64_t M, int64_t N) { return counter_bytes(32, N) + M * N * 4; }
+
+void set_sm_limit(int sms) { g_sm_limit = sms > 0 ? sms : 0; }
+
+// Reads (and optionally clears) the status word the kernels of this file set
+// when a bounded wait gives up.  Synchronises the device.
+int device_status(int* status, bool reset) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    set_error("cudaDeviceSynchronize failed: %s", cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  int v = 0;
+  e = cudaMemcpyFromSymbol(&v, ti_kernel_status, sizeof(int));
+  if (e != cudaSuccess) {
+    set_error("cudaMemcpyFromSymbol failed: %s", cudaGetErrorString(e));
+    return TI_E_CUDA;
+  }
+  if (reset && v != 0) {
+    // A kernel whose wait gave up may have left partial sums and tile counters in the split-K scratch,
+    // which every later launch expects to find all zero: clear the built-in array along with the word
+    // (the device is idle here; a caller-provided workspace must be cleared by its owner).
+    const int zero = 0;
+    cudaMemcpyToSymbol(ti_kernel_status, &zero, sizeof(int));
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+      std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+      if (g_static_scratch_ptr[dev] != nullptr) {
+        cudaMemset(g_static_scratch_ptr[dev], 0, static_cast<size_t>(kStaticScratchBytes));
+        cudaDeviceSynchronize();
+      }
+    }
+  }
+  *status = v;
+  return TI_OK;
+}
 
 }  // namespace ti
 

@@ -495,6 +495,46 @@ struct PeerPtrs {
   void* p[8];
 };
 
+// Synchronisation folded into the reduce kernel (n == 0: none, the caller brackets the kernel with
+// tp_barrier launches instead).  Every rank owns a pad of 16 32-bit words per channel in
+// peer-accessible memory: word [r] = "rank r's partial sums have arrived in my stage", word [8 + r] =
+// "rank r's reduce kernel is complete".  Both carry an epoch that grows by one per exchange.
+struct ExchangeSync {
+  void* pads[8];   // pads[t] = rank t's pad
+  int rank, n;
+  uint32_t epoch;
+  int* counter;    // CTAs of this launch that have finished; zero between launches
+  int* status;     // the library's status word
+  unsigned long long limit_ns;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Waits until *p has reached `epoch` (wrap-around safe).  Bounded: after limit_ns the status word is
+// set to 105 and the wait ends; once the status word is non-zero no wait of this process blocks.
+__device__ __forceinline__ void wait_epoch_sys(const uint32_t* p, uint32_t epoch, int* status,
+                                               unsigned long long limit_ns) {
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if (static_cast<int>(v - epoch) >= 0) return;
+    if ((it & 63) == 63) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
+        atomicCAS(status, 0, 105);
+        return;
+      }
+    }
+  }
+}
+
 // Second half of a row-parallel linear under tensor parallelism, for the rows this
 // rank owns: `stage` holds one int32 partial-sum slab per rank ([n_partials][rows][H],
 // written by the ranks' GEMM epilogues through peer stores).  Per row:
@@ -509,19 +549,33 @@ tp_reduce_layernorm_q_kernel(const int32_t* __restrict__ stage, int n_partials, 
                              float scale, const float* __restrict__ in_bias,
                              const float* __restrict__ res, const float* __restrict__ gamma,
                              const float* __restrict__ beta, float eps, float* __restrict__ res_out,
-                             PeerPtrs q_dst, int n_dst, long long q_row_offset, int H) {
+                             PeerPtrs q_dst, int n_dst, long long q_row_offset, int H, const ExchangeSync sync) {
   __shared__ float scratch[32];
   const long long row = blockIdx.x;
   const int h4 = H >> 2;
+  if (sync.n > 0) {
+    // Arrival: the copies that brought my partial sums into the peers' stages precede this kernel in
+    // stream order, so any CTA may announce them; a few CTAs spread over the grid do (the stores are
+    // idempotent).  Then every CTA waits until all ranks' partial sums of its rows are in place.
+    if (threadIdx.x < sync.n) {
+      if ((blockIdx.x & 63) == 0) {
+        __threadfence_system();
+        st_release_sys(static_cast<uint32_t*>(sync.pads[threadIdx.x]) + sync.rank, sync.epoch);
+      }
+      wait_epoch_sys(static_cast<const uint32_t*>(sync.pads[sync.rank]) + threadIdx.x, sync.epoch, sync.status,
+                     sync.limit_ns);
+    }
+    __syncthreads();
+  }
   float4 v[VPT];
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
     const int i = threadIdx.x + j * THREADS;
     if (i < h4) {
       const int32_t* ir = stage + row * H + 4 * i;
-      int4 a = *reinterpret_cast<const int4*>(ir);
+      int4 a = __ldcg(reinterpret_cast<const int4*>(ir));
       for (int s = 1; s < n_partials; ++s) {
-        const int4 b = *reinterpret_cast<const int4*>(ir + s * partial_stride);
+        const int4 b = __ldcg(reinterpret_cast<const int4*>(ir + s * partial_stride));
         a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
       }
       const float4 r = *reinterpret_cast<const float4*>(res + row * H + 4 * i);
@@ -566,6 +620,26 @@ tp_reduce_layernorm_q_kernel(const int32_t* __restrict__ stage, int n_partials, 
                                         __fmaf_rn((v[j].w - mean) * rstd, g.w, b.w));
       for (int d = 0; d < n_dst; ++d)
         *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(q_dst.p[d]) + qoff + 4 * i) = packed;
+    }
+  }
+  if (sync.n > 0) {
+    // Completion: the CTA that finishes last on this rank tells every rank so, then waits until every
+    // rank has said the same.  When this kernel ends, all ranks' int8 rows are in this rank's
+    // activation buffer and no rank reads its stage any more (the next exchange may overwrite it).
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const int done = atomicAdd(sync.counter, 1);
+      if (done == static_cast<int>(gridDim.x) - 1) {
+        *sync.counter = 0;
+        __threadfence_system();
+        for (int t = 0; t < sync.n; ++t)
+          st_release_sys(static_cast<uint32_t*>(sync.pads[t]) + 8 + sync.rank, sync.epoch);
+        for (int t = 0; t < sync.n; ++t)
+          wait_epoch_sys(static_cast<const uint32_t*>(sync.pads[sync.rank]) + 8 + t, sync.epoch, sync.status,
+                         sync.limit_ns);
+        __threadfence_system();
+      }
     }
   }
 }
@@ -802,10 +876,33 @@ int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch
 int tp_reduce_layernorm_q(const int32_t* stage, int n_partials, int64_t partial_stride, float scale,
                           const float* in_bias, const float* res, const float* gamma, const float* beta,
                           float eps, float* res_out, void* const* q_dst, int n_dst, int64_t q_row_offset,
-                          int64_t rows, int64_t H, cudaStream_t stream) {
+                          int64_t rows, int64_t H, const TpSync* ts, cudaStream_t stream) {
   if (rows < 0 || H <= 0 || n_partials < 1 || n_partials > 8 || n_dst < 1 || n_dst > 8) {
     set_error("tp_reduce_layernorm_q: bad shape");
     return TI_E_INVALID;
+  }
+  ExchangeSync sync = {};
+  if (ts != nullptr) {
+    if (ts->n < 1 || ts->n > 8 || ts->rank < 0 || ts->rank >= ts->n || !ts->pads || !ts->counter || !ts->status ||
+        rows == 0) {
+      set_error("tp_reduce_layernorm_q: bad synchronisation arguments (1..8 ranks, rows > 0)");
+      return TI_E_INVALID;
+    }
+    int64_t limit_ms = ts->limit_ms <= 0 ? 2000 : ts->limit_ms;
+    if (limit_ms > 60000) limit_ms = 60000;
+    for (int i = 0; i < ts->n; ++i) {
+      if (!ts->pads[i] || (reinterpret_cast<uintptr_t>(ts->pads[i]) & 3)) {
+        set_error("tp_reduce_layernorm_q: bad pad pointer %d", i);
+        return TI_E_INVALID;
+      }
+      sync.pads[i] = ts->pads[i];
+    }
+    sync.rank = ts->rank;
+    sync.n = ts->n;
+    sync.epoch = ts->epoch;
+    sync.counter = ts->counter;
+    sync.status = ts->status;
+    sync.limit_ns = static_cast<unsigned long long>(limit_ms) * 1000000ull;
   }
   if (rows == 0) return TI_OK;
   const int h4 = static_cast<int>(H / 4);
@@ -829,19 +926,22 @@ int tp_reduce_layernorm_q(const int32_t* stage, int n_partials, int64_t partial_
     return check_launch("tp_reduce_layernorm_q", [&] {
       tp_reduce_layernorm_q_kernel<128, 1><<<grid, 128, 0, stream>>>(
           stage, n_partials, partial_stride, scale, in_bias, res, gamma, beta, eps, res_out, dst, n_dst,
-          q_row_offset, static_cast<int>(H));
+          q_row_offset, static_cast<int>(H), sync);
     });
   const int vpt = (h4 + 255) / 256;
   int rc = TI_OK;
   TI_VPT_SWITCH(vpt, rc = check_launch("tp_reduce_layernorm_q", [&] {
                   tp_reduce_layernorm_q_kernel<256, VPT><<<grid, 256, 0, stream>>>(
                       stage, n_partials, partial_stride, scale, in_bias, res, gamma, beta, eps, res_out, dst,
-                      n_dst, q_row_offset, static_cast<int>(H));
+                      n_dst, q_row_offset, static_cast<int>(H), sync);
                 }));
   return rc;
 }
 
-int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_word, cudaStream_t stream) {
+int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_word, int64_t limit_ms,
+               cudaStream_t stream) {
+  if (limit_ms <= 0) limit_ms = 2000;
+  if (limit_ms > 60000) limit_ms = 60000;  // never more than a minute: a wait must not look like a hang
   if (n < 1 || n > 8 || rank < 0 || rank >= n || !pads || !status_word) {
     set_error("tp_barrier: bad arguments");
     return TI_E_INVALID;
@@ -855,7 +955,8 @@ int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_w
     }
   }
   return check_launch("tp_barrier", [&] {
-    tp_barrier_kernel<<<1, 32, 0, stream>>>(p, rank, n, epoch, status_word, 2000000000ull);
+    tp_barrier_kernel<<<1, 32, 0, stream>>>(p, rank, n, epoch, status_word,
+                                            static_cast<unsigned long long>(limit_ms) * 1000000ull);
   });
 }
 

@@ -22,11 +22,24 @@ int softmax_q(const float* scores, const float* mask, int8_t* out, int64_t batch
               int64_t T, int64_t S, int64_t lds, int64_t ldo, int causal, cudaStream_t stream);
 
 // Tensor-parallel exchange kernels (see the kernels in norm_quant.cu).
+// Optional synchronisation folded into tp_reduce_layernorm_q (nullptr: none): the kernel announces this
+// rank's partial sums to all ranks, waits for theirs, reduces, and ends only when every rank's reduction
+// is complete.  pads[i] = rank i's pad of 16 zero-initialised 32-bit words (peer accessible); epoch grows
+// by one per call; counter = a zero-initialised int in this GPU's memory; waits are bounded by limit_ms.
+struct TpSync {
+  void* const* pads;
+  int rank, n;
+  uint32_t epoch;
+  int* counter;
+  int* status;
+  int64_t limit_ms;
+};
 int tp_reduce_layernorm_q(const int32_t* stage, int n_partials, int64_t partial_stride, float scale,
                           const float* in_bias, const float* res, const float* gamma, const float* beta,
                           float eps, float* res_out, void* const* q_dst, int n_dst, int64_t q_row_offset,
-                          int64_t rows, int64_t H, cudaStream_t stream);
-int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_word, cudaStream_t stream);
+                          int64_t rows, int64_t H, const TpSync* sync, cudaStream_t stream);
+int tp_barrier(void* const* pads, int rank, int n, uint32_t epoch, int* status_word, int64_t limit_ms,
+               cudaStream_t stream);
 
 // int8 v [B, T, H, D] (token rows ld_in elements apart) -> vt [B, H, D, ld_out], written at
 // columns [col0, col0 + T).

@@ -96,7 +96,11 @@ _c_softmax_q = _sig("ti_softmax_q", [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _
 _c_tp_reduce_ln_q = _sig("ti_tp_reduce_layernorm_q",
                           [_ptr, _i32, _i64, _f32, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, ctypes.POINTER(_ptr), _i32,
                            _i64, _i64, _i64, _ptr])
-_c_tp_barrier = _sig("ti_tp_barrier", [ctypes.POINTER(_ptr), _i32, _i32, ctypes.c_uint32, _ptr])
+_c_tp_barrier = _sig("ti_tp_barrier_limit", [ctypes.POINTER(_ptr), _i32, _i32, ctypes.c_uint32, _i64, _ptr])
+_c_tp_exchange_reduce_ln_q = _sig("ti_tp_exchange_reduce_layernorm_q",
+                                  [_ptr, _i32, _i64, _f32, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, ctypes.POINTER(_ptr),
+                                   _i32, _i64, _i64, _i64, ctypes.POINTER(_ptr), _i32, _i32, ctypes.c_uint32, _ptr,
+                                   _i64, _ptr])
 _c_decode_attention = _sig("ti_decode_attention_s8",
                            [_ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _f32, _f32, _ptr, _i64, _ptr])
 _c_advance_position = _sig("ti_advance_position", [_ptr, _i32, _ptr])
@@ -492,11 +496,37 @@ def tp_reduce_layernorm_q(stage, n_partials, partial_stride, scale, bias, residu
     return out
 
 
-def tp_barrier(pad_ptrs, rank, epoch, device):
-    """Stream-ordered barrier over the ranks owning the pads at pad_ptrs (ti_tp_barrier)."""
+def tp_exchange_reduce_layernorm_q(stage, n_partials, partial_stride, scale, bias, residual, gamma, beta, epsilon,
+                                   q_dst_ptrs, q_row_offset, pad_ptrs, rank, epoch, counter, limit_ms=2000):
+    """tp_reduce_layernorm_q with the exchange's synchronisation inside the kernel
+    (ti_tp_exchange_reduce_layernorm_q): announces this rank's partial sums, waits for all ranks', reduces,
+    and returns (in stream order) only when every rank's reduction is complete.  `counter`: an int32 CUDA
+    tensor with one zero element, reserved for these calls."""
+    _require(stage, "stage", torch.int32)
+    _require(residual, "residual", torch.float32, 2)
+    _require(counter, "counter", torch.int32)
+    rows, h = residual.shape
+    g, b = _affine(gamma, beta, h, residual.device)
+    ib = _bias_vector(bias, h, torch.float32, residual.device)
+    out = torch.empty_like(residual)
+    arr = (_ptr * len(q_dst_ptrs))(*q_dst_ptrs)
+    pads = (_ptr * len(pad_ptrs))(*pad_ptrs)
+    with _on_device(residual.device):
+        rc = _c_tp_exchange_reduce_ln_q(stage.data_ptr(), n_partials, partial_stride, float(scale), ib.data_ptr(),
+                                        residual.data_ptr(), g.data_ptr(), b.data_ptr(), float(epsilon),
+                                        out.data_ptr(), arr, len(q_dst_ptrs), q_row_offset, rows, h, pads, rank,
+                                        len(pad_ptrs), epoch & 0xFFFFFFFF, counter.data_ptr(), int(limit_ms),
+                                        _stream_ptr(residual.device))
+    _check(rc)
+    return out
+
+
+def tp_barrier(pad_ptrs, rank, epoch, device, limit_ms=2000):
+    """Stream-ordered barrier over the ranks owning the pads at pad_ptrs (ti_tp_barrier_limit); the wait
+    gives up after limit_ms and sets the status word."""
     arr = (_ptr * len(pad_ptrs))(*pad_ptrs)
     with _on_device(device):
-        rc = _c_tp_barrier(arr, rank, len(pad_ptrs), epoch & 0xFFFFFFFF, _stream_ptr(device))
+        rc = _c_tp_barrier(arr, rank, len(pad_ptrs), epoch & 0xFFFFFFFF, int(limit_ms), _stream_ptr(device))
     _check(rc)
 
 
@@ -581,7 +611,15 @@ def set_sm_limit(sms):
 
 def device_status(reset=True):
     """Synchronises the current device and returns the kernels' status word
-    (0 = ok; otherwise the code of the first in-kernel wait that timed out)."""
+    (0 = ok; otherwise the code of the first in-kernel wait that timed out).
+    With reset, a non-zero word is cleared and so is the split-K scratch of the current device (a
+    launch that gave up may have left partial sums and counters in it, and every later small-M
+    GEMM expects it all zero)."""
     v = ctypes.c_int(0)
     _check(_c_device_status(ctypes.byref(v), 1 if reset else 0))
+    if reset and v.value != 0:
+        ws = _workspaces.get(torch.cuda.current_device())
+        if ws is not None:
+            ws.zero_()
+            torch.cuda.synchronize(ws.device)
     return v.value

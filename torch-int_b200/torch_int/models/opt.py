@@ -65,6 +65,11 @@ class Int8OPTConfig:
             self.word_embed_proj_dim = self.hidden_size
 
 
+# TI_TP_CHECK_EVERY_PASS=1: read the kernels' status word (a device synchronisation and one small
+# collective) after EVERY tensor-parallel forward pass, not only after the first one of a workspace.
+_CHECK_EVERY_PASS = os.environ.get("TI_TP_CHECK_EVERY_PASS", "0") == "1"
+
+
 def _round_up(v, m):
     return (v + m - 1) // m * m
 
@@ -537,18 +542,20 @@ class Int8OPTDecoder(nn.Module):
 
         def exchange(c, scale, bias, ln, tag):
             """On the communication stream(s).  Peer-memory form: this rank's partial sums go into
-            the owners' stage slabs (copy engines, or already stored there by the GEMM epilogue);
-            barrier; one kernel sums the slabs of my rows, applies scale/bias/residual/LayerNorm/
-            quantise and stores the int8 rows into every rank's activation buffer; barrier.
-            NCCL form: reduce-scatter -> fused LayerNorm kernel -> all-gather."""
+            the owners' stage slabs (copy engines, or already stored there by the GEMM epilogue), then
+            ONE kernel announces them, waits for all ranks', sums the slabs of my rows, applies scale/
+            bias/residual/LayerNorm/quantise, stores the int8 rows into every rank's activation buffer
+            and ends when every rank has done so (tp.fused_sync; otherwise the same steps as barrier ->
+            reduce kernel -> barrier).  NCCL form: reduce-scatter -> fused LayerNorm kernel -> all-gather."""
             done[c].record(compute)
             with torch.cuda.stream(comm):
                 comm.wait_event(done[c])
                 if ws is not None:
-                    with tp.span("push+barrier", "exchange.copy", comm, group=c, at=tag):
+                    with tp.span("push", "exchange.copy", comm, group=c, at=tag):
                         if tp.peer_mode == "copy":
                             ws.push_partials(c, acc[c])
-                        ws.barrier(0)
+                        if not tp.fused_sync:
+                            ws.barrier(0)
                     if comm2 is not comm:
                         copied[c].record(comm)
                 else:
@@ -561,11 +568,15 @@ class Int8OPTDecoder(nn.Module):
                 with torch.cuda.stream(comm2):
                     if comm2 is not comm:
                         comm2.wait_event(copied[c])
-                    with tp.span("reduce+ln", "exchange.reduce", comm2, group=c, at=tag):
-                        res[c] = C.tp_reduce_layernorm_q(ws.stage[c], n, ms * e, scale, bias, res[c], ln.weight,
-                                                         ln.bias, ln.eps, ws.q_dst_ptrs(c), rank * ms)
-                    with tp.span("barrier", "exchange.reduce", comm2, group=c, at=tag):
-                        ws.barrier(1 if comm2 is not comm else 0)
+                    if tp.fused_sync:
+                        with tp.span("sync+reduce+ln+sync", "exchange.reduce", comm2, group=c, at=tag):
+                            res[c] = ws.exchange_reduce(c, scale, bias, res[c], ln)
+                    else:
+                        with tp.span("reduce+ln", "exchange.reduce", comm2, group=c, at=tag):
+                            res[c] = C.tp_reduce_layernorm_q(ws.stage[c], n, ms * e, scale, bias, res[c], ln.weight,
+                                                             ln.bias, ln.eps, ws.q_dst_ptrs(c), rank * ms)
+                        with tp.span("barrier", "exchange.reduce", comm2, group=c, at=tag):
+                            ws.barrier(1 if comm2 is not comm else 0)
                     ready[c].record(comm2)
 
         def row_parallel(c, x2d, weight, k):
@@ -603,6 +614,10 @@ class Int8OPTDecoder(nn.Module):
                     res[c].record_stream(comm)  # allocated on the second stream, last read on this one
                 tp.all_gather_into(out[c * bc:(c + 1) * bc].view(mc, e), res[c])
         compute.wait_stream(comm)
+        if ws is not None and (not ws.checked or _CHECK_EVERY_PASS):
+            # a barrier whose bounded wait ran out leaves the activations unsynchronised: find out now
+            # (all ranks together) instead of returning wrong logits silently
+            tp.check_exchange(ws, dev)
         return out
 
     @torch.no_grad()

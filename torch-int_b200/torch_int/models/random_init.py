@@ -43,7 +43,9 @@ def init_random_(model: Int8OPTForCausalLM, seed: int = 0, consistent: bool = Tr
     """Fills `model` in place.  consistent=True draws every FULL tensor from a CPU
     generator keyed by (seed, layer, name) and keeps this rank's slice, so all
     tensor-parallel layouts hold the same model; consistent=False draws each rank's
-    slice directly on its device (fast, for large benchmark models)."""
+    slice of the split int8 weights directly on its device (fast, for large benchmark models).
+    The replicated parameters (scales, LayerNorm, fp32 biases, embeddings) depend on `seed` alone
+    in both modes: ranks that pass the same seed hold one coherent model."""
     dec = model.model.decoder
     cfg, tp = model.config, dec.tp
     dev = dec.embed_tokens.weight.device
@@ -52,6 +54,13 @@ def init_random_(model: Int8OPTForCausalLM, seed: int = 0, consistent: bool = Tr
 
     def jitter(li, name):
         return float(0.7 + 0.6 * torch.rand((), generator=_cpu_gen(seed, li, name, "jitter")))
+
+    # consistent=False: this rank's slices come from a device generator keyed by (seed, rank), so that
+    # a run is reproducible and the ranks hold different slices of one model
+    dev_gen = None
+    if not consistent and torch.device(dev).type == "cuda":
+        dev_gen = torch.Generator(device=dev)
+        dev_gen.manual_seed(zlib.crc32(repr((seed, "slices", tp.rank)).encode()))
 
     def s8(shape_full, li, name, kind):
         """kind: 'rows' (column-parallel weight), 'cols' (row-parallel weight), 'vec' ([1,N] bias of a
@@ -68,7 +77,7 @@ def init_random_(model: Int8OPTForCausalLM, seed: int = 0, consistent: bool = Tr
             shape[0] //= tp.size
         elif kind in ("cols", "vec"):
             shape[-1] //= tp.size
-        return torch.randint(-127, 128, shape, dtype=torch.int8, device=dev)
+        return torch.randint(-127, 128, shape, dtype=torch.int8, device=dev, generator=dev_gen)
 
     def f32(shape, li, name, std, mean=0.0):
         t = torch.randn(shape, generator=_cpu_gen(seed, li, name)) * std + mean

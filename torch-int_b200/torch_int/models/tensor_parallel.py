@@ -104,6 +104,9 @@ class TensorParallel:
         # exchange back to back.  2: the copies (+ first barrier) and the reduce kernel (+ second barrier)
         # run on two streams, so the copies of the next group overlap the reduction of this one.
         self.comm_streams = int(os.environ.get("TI_TP_COMM_STREAMS", "1"))
+        # True: the two barriers of an exchange are folded into the reduce kernel (one launch per
+        # exchange after the copies); False: barrier kernel -> reduce kernel -> barrier kernel
+        self.fused_sync = os.environ.get("TI_TP_FUSED_SYNC", "1") != "0"
         # a StreamTrace while a forward pass is being traced, else None
         self.trace: Optional[StreamTrace] = None
         # language-model head split by vocabulary rows: each rank multiplies with its 1/size of the
@@ -188,23 +191,52 @@ class TensorParallel:
         # [size, tokens, V/size] -> [tokens, size * V/size]
         return gathered.view(self.size, tokens, v1 - v0).permute(1, 0, 2).reshape(*lead, v)
 
+    def agree_max(self, value: int, device) -> int:
+        """Maximum of a small integer over the ranks (one collective): the way every rank reaches the
+        same decision from per-rank observations."""
+        if self.size == 1:
+            return int(value)
+        t = torch.tensor([int(value)], dtype=torch.int32, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return int(t.item())
+
     def peer_workspace(self, chunks: int, mc: int, e: int, device):
         """Peer-accessible buffers for the fused exchange of the pipelined layer loop, or
-        None when symmetric memory is unavailable (then NCCL collectives are used)."""
+        None when symmetric memory is unavailable (then NCCL collectives are used).
+
+        Every rank must call this at the same point: whether the peer-memory path is used is decided
+        COLLECTIVELY.  A rank whose allocation or set-up failed reports that through a reduction over
+        the ranks, and then all ranks fall back together; a rank never switches paths on its own (its
+        peers would wait for it in a barrier while it waits for them in a collective)."""
         if not self.use_peer_memory:
             return None
         key = (chunks, mc, e, torch.device(device).index)
         ws = self._workspaces.get(key)
         if ws is None:
-            try:
-                ws = PeerWorkspace(self, chunks, mc, e, device)
-            except Exception as exc:  # noqa: BLE001 - any failure means "fall back to NCCL"
+            ws = PeerWorkspace.create(self, chunks, mc, e, device)
+            if ws is None:
                 import warnings
-                warnings.warn(f"tensor parallel: peer memory unavailable ({exc}); using NCCL collectives")
+                warnings.warn("tensor parallel: peer memory unavailable on at least one rank; "
+                              "all ranks use NCCL collectives")
                 self.use_peer_memory = False
                 return None
             self._workspaces[key] = ws
         return ws
+
+    def check_exchange(self, ws, device):
+        """Reads the kernels' status word, agreed over the ranks, after a forward pass that used the
+        peer-memory exchange `ws`.  Non-zero (a bounded wait of a barrier ran out on some rank: the
+        activations of that pass are not trustworthy) switches ALL ranks to the NCCL exchange and raises.
+        Called for the first pass of every workspace, and for every pass when TI_TP_CHECK_EVERY_PASS=1."""
+        from .. import _CUDA as C
+        status = self.agree_max(C.device_status(reset=True), device)
+        ws.checked = True
+        if status != 0:
+            self.use_peer_memory = False
+            self._workspaces.clear()
+            raise RuntimeError(f"tensor parallel: the peer-memory exchange reported status {status} (a bounded wait "
+                               "ran out); the results of this pass are invalid.  All ranks now use NCCL collectives: "
+                               "repeat the call.")
 
     # ------------------------------------------------------------- weight sharding
     def _rows(self, t: torch.Tensor) -> torch.Tensor:
@@ -268,30 +300,54 @@ class PeerWorkspace:
     Allocated with torch's symmetric memory (cuMem mappings exchanged between the processes);
     all traffic is plain peer loads/stores issued by this library's kernels."""
 
-    def __init__(self, tp: "TensorParallel", chunks: int, mc: int, e: int, device):
+    @classmethod
+    def create(cls, tp: "TensorParallel", chunks: int, mc: int, e: int, device):
+        """Collective constructor: returns the workspace on every rank, or None on every rank.  Each
+        phase that can fail on one rank alone (allocation, mapping, the barrier preflight) ends with a
+        reduction of a failure flag over the ranks, so that no rank is left waiting for one that gave up."""
+        ws = object.__new__(cls)
+        ws.checked = False
+        dev = torch.device(device)
+        err = None
+        try:
+            ws._allocate(tp, chunks, mc, e, dev)
+        except Exception as exc:  # noqa: BLE001 - any local failure means "all ranks fall back"
+            err = exc
+        if tp.agree_max(0 if err is None else 1, dev) != 0:
+            return None
+        try:
+            ws._map_and_preflight()
+        except Exception as exc:  # noqa: BLE001
+            err = exc
+        if tp.agree_max(0 if err is None else 1, dev) != 0:
+            return None
+        return ws
+
+    def _allocate(self, tp, chunks, mc, e, device):
         import torch.distributed._symmetric_memory as symm
         from .. import _CUDA as C
         self._C = C
         n = tp.size
         ms = mc // n
-        self.tp, self.chunks, self.mc, self.ms, self.e, self.device = tp, chunks, mc, ms, e, torch.device(device)
+        self.tp, self.chunks, self.mc, self.ms, self.e, self.device = tp, chunks, mc, ms, e, device
         stage_bytes = chunks * n * ms * e * 4
         h8_bytes = chunks * mc * e
+        self.stage_bytes, self.h8_bytes = stage_bytes, h8_bytes
         self.stage_off = 0
         self.h8_off = (stage_bytes + 255) // 256 * 256
         self.pad_off = (self.h8_off + h8_bytes + 255) // 256 * 256
         total = self.pad_off + 256
-        group = tp.group if tp.group is not None else dist.group.WORLD
-        if hasattr(symm, "enable_symm_mem_for_group"):
-            try:
-                symm.enable_symm_mem_for_group(group.group_name)
-            except Exception:  # noqa: BLE001 - newer releases enable it implicitly
-                pass
+        self.group = tp.group if tp.group is not None else dist.group.WORLD
         self.buf = symm.empty(total, dtype=torch.uint8, device=self.device)
+
+    def _map_and_preflight(self):
+        import torch.distributed._symmetric_memory as symm
+        C, tp, group = self._C, self.tp, self.group
+        chunks, n, ms, e, mc = self.chunks, tp.size, self.ms, self.e, self.mc
         self.handle = symm.rendezvous(self.buf, group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self.stage = self.buf[:stage_bytes].view(torch.int32).view(chunks, n, ms, e)
-        self.h8 = self.buf[self.h8_off:self.h8_off + h8_bytes].view(torch.int8).view(chunks, mc, e)
+        self.stage = self.buf[:self.stage_bytes].view(torch.int32).view(chunks, n, ms, e)
+        self.h8 = self.buf[self.h8_off:self.h8_off + self.h8_bytes].view(torch.int8).view(chunks, mc, e)
         self.buf[self.pad_off:].zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)  # every rank's pads are zero before the first barrier kernel
@@ -300,17 +356,24 @@ class PeerWorkspace:
         self.epochs = [0] * 4
         self.channel_pads = [[p + self.pad_off + 64 * ch for p in self.ptrs] for ch in range(4)]
         self.pad_ptrs = self.channel_pads[0]
-        # Preflight: a few barriers over the fresh pads.  If peer stores or loads do not work on this
-        # machine the (bounded) waits give up and set the status word; every rank then learns of it
-        # through one NCCL reduction and the caller falls back to NCCL collectives.
+        # CTA counters of the reduce kernel with folded-in synchronisation (one per channel)
+        self.counters = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # Preflight: a few barriers over the fresh pads, with a generous time limit (the first kernels
+        # of a process load lazily, so the ranks may reach them seconds apart).  If peer stores or
+        # loads do not work on this machine the (bounded) waits give up and set the status word; every
+        # rank then learns of it through the reduction in create().
         for _ in range(3):
-            self.barrier()
-        flag = torch.tensor([C.device_status(reset=True)], dtype=torch.int32, device=self.device)
-        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
-        if int(flag.item()) != 0:
-            raise RuntimeError(f"peer-memory barrier preflight failed (status {int(flag.item())})")
+            self.barrier(limit_ms=self.FIRST_LIMIT_MS)
+        status = C.device_status(reset=True)
+        if status != 0:
+            raise RuntimeError(f"peer-memory barrier preflight failed (status {status})")
         # every rank's stage as a tensor of this process (peer mappings), for contiguous peer copies
         self.peer_stage = [self.handle.get_buffer(o, (chunks, n, ms, e), torch.int32, 0) for o in range(n)]
+
+    # time limits of a barrier's wait: the first barriers of a workspace tolerate start-up skew
+    # between the ranks; TI_TP_BARRIER_LIMIT_MS sets the limit of all later ones
+    FIRST_LIMIT_MS = 20000
+    LIMIT_MS = int(os.environ.get("TI_TP_BARRIER_LIMIT_MS", "2000"))
 
     def scatter_ptrs(self, c):
         """Where the GEMM epilogue writes row block o of chunk c: slab [my rank] of owner o's stage."""
@@ -328,8 +391,25 @@ class PeerWorkspace:
             o = (r + 1 + i) % self.tp.size  # start with the right-hand neighbour: spreads the link load
             self.peer_stage[o][c, r].copy_(acc[o * ms:(o + 1) * ms], non_blocking=True)
 
-    def barrier(self, channel: int = 0):
-        """Enqueues a bounded barrier over all ranks on the current stream.  All barriers of one
-        channel must be issued from one stream, in the same order on every rank."""
+    def exchange_reduce(self, c, scale, bias, residual, ln, channel: int = 2):
+        """The second half of an exchange as ONE kernel on the current stream (after the copies of
+        push_partials in stream order): announce, wait for all ranks, reduce + LayerNorm-quantise chunk
+        c's rows of this rank into every rank's activation buffer, wait until all ranks are complete.
+        Returns the new residual rows.  All calls of one channel come from one stream, in the same order
+        on every rank."""
         self.epochs[channel] += 1
-        self._C.tp_barrier(self.channel_pads[channel], self.tp.rank, self.epochs[channel], self.device)
+        limit_ms = self.LIMIT_MS if self.checked else self.FIRST_LIMIT_MS
+        return self._C.tp_exchange_reduce_layernorm_q(
+            self.stage[c], self.tp.size, self.ms * self.e, scale, bias, residual, ln.weight, ln.bias, ln.eps,
+            self.q_dst_ptrs(c), self.tp.rank * self.ms, self.channel_pads[channel], self.tp.rank,
+            self.epochs[channel], self.counters[channel:channel + 1], limit_ms=limit_ms)
+
+    def barrier(self, channel: int = 0, limit_ms: Optional[int] = None):
+        """Enqueues a bounded barrier over all ranks on the current stream.  All barriers of one
+        channel must be issued from one stream, in the same order on every rank.  Until the first
+        forward pass over this workspace has been checked, the generous start-up limit applies."""
+        self.epochs[channel] += 1
+        if limit_ms is None:
+            limit_ms = self.LIMIT_MS if self.checked else self.FIRST_LIMIT_MS
+        self._C.tp_barrier(self.channel_pads[channel], self.tp.rank, self.epochs[channel], self.device,
+                           limit_ms=limit_ms)
