@@ -358,8 +358,10 @@ class OptWorkload:
         if self.world == 1:
             return "none"
         if self.tp.use_peer_memory and self.tp._workspaces:
-            return (f"peer memory ({self.tp.peer_mode}): partial sums to the owners' slabs -> barrier -> "
-                    "reduce+LayerNorm kernel with peer stores -> barrier")
+            tail = ("one kernel: announce, wait for all ranks, reduce + LayerNorm-quantise with peer stores, wait for all ranks"
+                    if self.tp.fused_sync else "barrier -> reduce+LayerNorm kernel with peer stores -> barrier")
+            return (f"peer memory ({self.tp.peer_mode}): partial sums to the owners' slabs -> {tail}; "
+                    f"{self.tp.comm_streams} communication stream(s), {self.tp.max_chunks} sequence groups")
         return "NCCL reduce-scatter / all-gather on a communication stream"
 
     def ranks_agree(self):

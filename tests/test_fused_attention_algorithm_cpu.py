@@ -2,7 +2,8 @@
 tile in numpy float32 and compared with the oracle chain scores -> softmax -> x127 -> round -> context
 (torch_int/models/opt.py:131-181).  This pins the index arithmetic of the kernel (tile counts, causal limits
 with a cached prefix, ragged last tiles) and the claim that accumulating the row sum tile by tile with a
-running maximum moves the int8 context by at most one unit; it says nothing about the kernel's PTX."""
+running maximum (per column half, combined once) moves the int8 context by at most one unit; it says nothing
+about the kernel's PTX."""
 import numpy as np
 import pytest
 import torch
@@ -12,11 +13,14 @@ from oracle import w8a8 as O
 
 TILE = 128
 F = np.float32
+LOG2E = F(1.4426950408889634)
 
 
 def emulate(q, k, vt, past, alpha_qk, alpha_pv):
     """q [T,D], k [S,D], vt [D,S] int8 (one sequence, one head) -> int8 [T,D], following the kernel:
-    one CTA per 128 query rows, keys visited in tiles of 128 up to the last one any row of the CTA sees."""
+    one CTA per 128 query rows, keys visited in tiles of 128 up to the last one any row of the CTA sees;
+    the row sum is built from two per-thread partial sums (keys [0,64) and [64,128) of every tile) with
+    2^(x log2 e) as the exponential, every probability from expf and an exact division."""
     t_len, d = q.shape
     s_len = k.shape[0]
     out = np.zeros((t_len, d), dtype=np.int8)
@@ -39,17 +43,26 @@ def emulate(q, k, vt, past, alpha_qk, alpha_pv):
             cols = j * TILE + np.arange(TILE)
             return (F(alpha_qk) * acc.astype(F)).astype(F), cols[None, :] <= lim[:, None]
 
-        m = np.full(TILE, fmin, dtype=F)
-        l = np.zeros(TILE, dtype=F)
-        for j in range(nt):                                      # pass 1
+        # pass 1: two threads per row, each with a running maximum and sum over ITS 64 keys of every tile
+        mh = [np.full(TILE, fmin, dtype=F) for _ in range(2)]
+        lh = [np.zeros(TILE, dtype=F) for _ in range(2)]
+        for j in range(nt):
             s, vis = scores(j)
-            tmax = np.where(vis, s, fmin).max(axis=1).astype(F)
-            mn = np.maximum(m, tmax)
-            l = (l * np.exp((m - mn).astype(F)).astype(F)).astype(F)
-            with np.errstate(over="ignore"):             # rows past the end (nothing visible): masked by `vis`
-                e = np.where(vis, np.exp((s - mn[:, None]).astype(F)), F(0)).astype(F)
-            l = (l + e.sum(axis=1, dtype=F)).astype(F)
-            m = mn
+            for hf in range(2):
+                sl = slice(64 * hf, 64 * hf + 64)
+                sh, vh = s[:, sl], vis[:, sl]
+                any_vis = vh.any(axis=1)
+                tmax = np.where(vh, sh, fmin).max(axis=1).astype(F)
+                mn = np.where(any_vis, np.maximum(mh[hf], tmax), mh[hf]).astype(F)
+                with np.errstate(over="ignore", under="ignore"):
+                    lh[hf] = (lh[hf] * np.exp2(((mh[hf] - mn).astype(F) * LOG2E).astype(F)).astype(F)).astype(F)
+                    e = np.where(vh, np.exp2(((sh - mn[:, None]).astype(F) * LOG2E).astype(F)), F(0)).astype(F)
+                lh[hf] = (lh[hf] + e.sum(axis=1, dtype=F)).astype(F)
+                mh[hf] = mn
+        m = np.maximum(mh[0], mh[1])
+        with np.errstate(over="ignore", under="ignore", invalid="ignore"):
+            l = ((lh[0] * np.exp((mh[0] - m).astype(F)).astype(F)).astype(F) +
+                 (lh[1] * np.exp((mh[1] - m).astype(F)).astype(F)).astype(F)).astype(F)
         acc_o = np.zeros((TILE, d), dtype=np.int64)
         for j in range(nt):                                      # pass 2
             s, vis = scores(j)

@@ -14,12 +14,20 @@
 // (S^2, written and read) touch HBM; the price is computing Q.K^T twice, which the tensor cores
 // have room for (the kernel is bound by the exponentials).
 //
-// One CTA per (sequence, head, 128 query rows); 192 threads: warp 0 = TMA producer, warp 1 = MMA
-// issuer, warps 2-5 = softmax / epilogue (thread = query row, TMEM lane = row).  TMEM: 128 columns
-// S + up to 128 columns O = 256 of 512, shared memory 97 KB: two CTAs per SM, so one CTA's softmax
-// overlaps the other's MMAs and loads.  Only keys j <= t + past are visited (causal); an explicit
-// additive mask is not supported - callers with padding masks use the three-kernel path.
-// Every wait is bounded (2 s) and reports through the status word.
+// One CTA per (sequence, head, 128 query rows); 320 threads: warp 0 = TMA producer, warp 1 = MMA
+// issuer, warps 2-9 = softmax / epilogue.  Two threads share a query row (TMEM lane = row): one owns
+// keys [0, 64) of every tile, the other keys [64, 128); each keeps a running maximum and sum of its
+// keys, the two are combined once after pass 1.  A thread copies its 64 accumulators into registers
+// and releases S immediately, so the next Q.K^T runs while the exponentials of this tile are evaluated.
+// Key tiles entirely below the diagonal take a mask-free path.  TMEM: 128 columns S + up to 128
+// columns O = 256 of 512, shared memory 99 KB: two CTAs per SM.  Only keys j <= t + past are visited
+// (causal); an explicit additive mask is not supported - callers with padding masks use the
+// three-kernel path.  Every wait is bounded (2 s) and reports through the status word.
+//
+// Rounding: every probability is rne(127 * expf(s - m) / l) with IEEE-exact division (a multiply by
+// RN(1/l) plus two residual corrections); the row sum l is accumulated per thread with ex2.approx and
+// in tile order, so it can differ from a sequential expf sum in its last bits, which moves a
+// probability by one unit only where 127 * e / l sits on a rounding tie.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <float.h>
@@ -36,9 +44,12 @@ namespace {
 constexpr int TILE_ROWS = 128;             // query rows per CTA, keys per tile
 constexpr int TILE_BYTES = 128 * 128;      // one 128-row x 128-byte swizzled operand tile
 constexpr int NSLOT = 4;                   // ring of K / V^T tiles
-constexpr int ATT_THREADS = 192;
+constexpr int SOFTMAX_WARPS = 8;           // two threads per query row: each owns 64 of a tile's 128 keys
+constexpr int SOFTMAX_THREADS = SOFTMAX_WARPS * 32;
+constexpr int ATT_THREADS = 64 + SOFTMAX_THREADS;
 constexpr int TMEM_COLS = 256;
-constexpr int SMEM_BYTES = 1024 + (2 + NSLOT) * TILE_BYTES + 256;
+constexpr int STATS_BYTES = 2 * 2 * TILE_ROWS * 4;  // (m, l) of both column halves of every row
+constexpr int SMEM_BYTES = 1024 + (2 + NSLOT) * TILE_BYTES + STATS_BYTES + 256;
 
 enum : int {
   TI_ERR_ATT_RING_EMPTY = 121,  // producer waited for a free ring slot
@@ -67,6 +78,32 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// 2^x to about 2 ulp; used for the row sum only (every probability is formed with expf).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Four values, each already rounded to an integer, clamped to [-128, 127] and packed into bytes.
+__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d) {
+  uint32_t lo, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(lo) : "r"(d), "r"(c));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(lo));
+  return out;
+}
+
+// e / l rounded to nearest, given r = RN(1 / l): a product and two residual corrections (Markstein's
+// scheme) reproduce IEEE division for the operands that occur here (0 <= e <= 1 <= l, both normal
+// or e so small that the probability is 0 either way) without a reciprocal per element.
+__device__ __forceinline__ float div_by_row_sum(float e, float l, float r) {
+  float q = __fmul_rn(e, r);
+  float rem = __fmaf_rn(-q, l, e);
+  q = __fmaf_rn(rem, r, q);
+  rem = __fmaf_rn(-q, l, e);
+  return __fmaf_rn(rem, r, q);
+}
+
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -79,7 +116,8 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   uint8_t* sQ = smem;                     // [128 rows][128 B]  (D = 64: upper half of each row zero)
   uint8_t* sP = smem + TILE_BYTES;        // [128 rows][128 keys]
   uint8_t* ring = smem + 2 * TILE_BYTES;  // NSLOT tiles
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + NSLOT * TILE_BYTES);
+  float* stats = reinterpret_cast<float*>(ring + NSLOT * TILE_BYTES);  // [half][m | l][row]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + STATS_BYTES);
   uint64_t* full_bar = bars;              // [NSLOT]
   uint64_t* empty_bar = bars + NSLOT;     // [NSLOT]
   uint64_t* q_full = bars + 2 * NSLOT;
@@ -107,8 +145,8 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     }
     mbar_init(smem_u32(q_full), 1);
     mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(s_empty), 128);
-    mbar_init(smem_u32(p_full), 128);
+    mbar_init(smem_u32(s_empty), SOFTMAX_THREADS);
+    mbar_init(smem_u32(p_full), SOFTMAX_THREADS);
     mbar_init(smem_u32(p_empty), 1);
     mbar_init(smem_u32(o_full), 1);
     *abort_flag = 0;
@@ -177,7 +215,7 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       auto issue_s = [&]() {
         ok = mbar_wait_status(smem_u32(&full_bar[slot]), phase, abort_flag, p.status, TI_ERR_ATT_RING_FULL);
         if (!ok) return;
-        // the softmax warps have drained the previous S (the first wait passes at once)
+        // the softmax warps have copied the previous S into registers (the first wait passes at once)
         ok = mbar_wait_status(smem_u32(s_empty), (g & 1) ^ 1, abort_flag, p.status, TI_ERR_ATT_S_EMPTY);
         if (!ok) return;
         tc_fence_after();
@@ -210,123 +248,166 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     }
   } else {
     // --------------------------------------------------------- softmax and epilogue
+    // Two threads per query row: warps 2-5 own keys [0, 64) of every tile, warps 6-9 keys [64, 128).
+    // A thread copies its 64 accumulators into registers and releases S at once, so the tensor core
+    // computes the next S while the exponentials of this one run.
     const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int half = (warp - 2) >> 2;        // which 64 keys of a tile
     const int r = quarter * 32 + lane;       // row of the tile = TMEM lane
     const int rg = t0 + r;                   // row of the sequence
     const bool valid = rg < p.T;
     const int lim = valid ? rg + p.past : -1;  // last visible key
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_s + lane_off + half * 64;
     const float alpha = p.alpha_qk;
+    const bool alpha_neg = alpha < 0.f;
+    constexpr float kLog2e = 1.4426950408889634f;
     // the fp32 score exactly as the unfused path stores it: one rounded multiply (never contracted
     // into the following subtraction)
     auto score = [alpha](uint32_t acc) { return __fmul_rn(alpha, __int2float_rn(static_cast<int>(acc))); };
     float m = -FLT_MAX, l = 0.f;
     uint32_t g = 0;
     bool ok = true;
-    // ---- pass 1: row maximum and row sum
-#pragma unroll 1
-    for (int j = 0; j < nt && ok; ++j, ++g) {
+    uint32_t va[32], vb[32];
+    auto fetch_s = [&]() {
       ok = mbar_wait_status(smem_u32(s_full), g & 1, abort_flag, p.status, TI_ERR_ATT_S_FULL);
-      if (!ok) break;
+      if (!ok) return;
       tc_fence_after();
-      const int c0 = j * TILE_ROWS;
-      float tmax = -FLT_MAX;
+      tmem_ld_32x32(s_addr, va);
+      tmem_ld_32x32(s_addr + 32, vb);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(s_empty));
+      ++g;
+    };
+    // ---- pass 1: row maximum and row sum over this thread's keys
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-        tmem_ld_wait();
+    for (int j = 0; j < nt && ok; ++j) {
+      fetch_s();
+      if (!ok) break;
+      const int c0 = j * TILE_ROWS + half * 64;
+      const bool all_visible = c0 + 63 <= t0 + p.past;  // for every valid row of the CTA (uniform)
+      // the largest score = the score of the largest (alpha < 0: smallest) accumulator
+      int best = alpha_neg ? INT_MAX : INT_MIN;
+      bool any = all_visible;
+      if (all_visible) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          if (c0 + c * 32 + i <= lim) tmax = fmaxf(tmax, score(v[i]));
+          const int a0 = static_cast<int>(va[i]), a1 = static_cast<int>(vb[i]);
+          best = alpha_neg ? min(best, min(a0, a1)) : max(best, max(a0, a1));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (c0 + i <= lim) {
+            best = alpha_neg ? min(best, static_cast<int>(va[i])) : max(best, static_cast<int>(va[i]));
+            any = true;
+          }
+          if (c0 + 32 + i <= lim) {
+            best = alpha_neg ? min(best, static_cast<int>(vb[i])) : max(best, static_cast<int>(vb[i]));
+            any = true;
+          }
         }
       }
-      const float mn = fmaxf(m, tmax);
-      l *= expf(m - mn);
+      if (!any) continue;  // none of this thread's keys of this tile is visible to its row
+      const float mn = fmaxf(m, score(static_cast<uint32_t>(best)));
+      l *= ex2_approx((m - mn) * kLog2e);
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-        tmem_ld_wait();
+      if (all_visible) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const int col = c0 + c * 32 + i;
-          if (col <= lim) a0 += expf(score(v[i]) - mn);
-          if (col + 1 <= lim) a1 += expf(score(v[i + 1]) - mn);
-          if (col + 2 <= lim) a2 += expf(score(v[i + 2]) - mn);
-          if (col + 3 <= lim) a3 += expf(score(v[i + 3]) - mn);
+        for (int i = 0; i < 32; i += 2) {
+          a0 += ex2_approx((score(va[i]) - mn) * kLog2e);
+          a1 += ex2_approx((score(va[i + 1]) - mn) * kLog2e);
+          a2 += ex2_approx((score(vb[i]) - mn) * kLog2e);
+          a3 += ex2_approx((score(vb[i + 1]) - mn) * kLog2e);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          if (c0 + i <= lim) a0 += ex2_approx((score(va[i]) - mn) * kLog2e);
+          if (c0 + i + 1 <= lim) a1 += ex2_approx((score(va[i + 1]) - mn) * kLog2e);
+          if (c0 + 32 + i <= lim) a2 += ex2_approx((score(vb[i]) - mn) * kLog2e);
+          if (c0 + 33 + i <= lim) a3 += ex2_approx((score(vb[i + 1]) - mn) * kLog2e);
         }
       }
       l += (a0 + a1) + (a2 + a3);
       m = mn;
-      tc_fence_before();
-      mbar_arrive(smem_u32(s_empty));
     }
+    // ---- the row's maximum and sum over all keys: combine the two halves (in a fixed order, so that
+    //      both threads of a row hold identical values)
+    stats[(half * 2 + 0) * TILE_ROWS + r] = m;
+    stats[(half * 2 + 1) * TILE_ROWS + r] = l;
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+    {
+      const float m0 = stats[0 * TILE_ROWS + r], l0 = stats[1 * TILE_ROWS + r];
+      const float m1 = stats[2 * TILE_ROWS + r], l1 = stats[3 * TILE_ROWS + r];
+      m = fmaxf(m0, m1);
+      l = l0 * expf(m0 - m) + l1 * expf(m1 - m);
+    }
+    const float rl = __frcp_rn(l);
     // ---- pass 2: probabilities -> P tile -> O += P . V
     uint8_t* prow = sP + r * 128;
     const int sw = r & 7;
 #pragma unroll 1
-    for (int j = 0; j < nt && ok; ++j, ++g) {
-      ok = mbar_wait_status(smem_u32(s_full), g & 1, abort_flag, p.status, TI_ERR_ATT_S_FULL);
+    for (int j = 0; j < nt && ok; ++j) {
+      fetch_s();
       if (!ok) break;
+      const int c0 = j * TILE_ROWS + half * 64;
+      const bool all_visible = c0 + 63 <= t0 + p.past;
+      uint32_t w[16];
+      auto prob = [&](uint32_t acc) {
+        const float e = expf(score(acc) - m);
+        return __float2int_rn(__fmul_rn(div_by_row_sum(e, l, rl), 127.f));
+      };
+      if (all_visible) {
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          w[q4] = pack_sat_s8x4(prob(va[q4 * 4]), prob(va[q4 * 4 + 1]), prob(va[q4 * 4 + 2]), prob(va[q4 * 4 + 3]));
+          w[8 + q4] = pack_sat_s8x4(prob(vb[q4 * 4]), prob(vb[q4 * 4 + 1]), prob(vb[q4 * 4 + 2]), prob(vb[q4 * 4 + 3]));
+        }
+      } else {
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          int x[4], y[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            x[i] = (c0 + q4 * 4 + i <= lim) ? prob(va[q4 * 4 + i]) : 0;
+            y[i] = (c0 + 32 + q4 * 4 + i <= lim) ? prob(vb[q4 * 4 + i]) : 0;
+          }
+          w[q4] = pack_sat_s8x4(x[0], x[1], x[2], x[3]);
+          w[8 + q4] = pack_sat_s8x4(y[0], y[1], y[2], y[3]);
+        }
+      }
       // P_{j-1} has been consumed by its MMAs (the first wait passes at once)
       ok = mbar_wait_status(smem_u32(p_empty), (j & 1) ^ 1, abort_flag, p.status, TI_ERR_ATT_P_EMPTY);
       if (!ok) break;
-      tc_fence_after();
-      const int c0 = j * TILE_ROWS;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-        tmem_ld_wait();
-        uint32_t w[8];
+      // 16-byte chunk q of row r lives at chunk position q ^ (r % 8) (128-byte swizzle); this thread
+      // owns chunks 4*half .. 4*half + 3
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          uint32_t packed = 0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int col = c0 + c * 32 + q4 * 4 + i;
-            int pv = 0;
-            if (col <= lim) {
-              const float e = expf(score(v[q4 * 4 + i]) - m);
-              pv = min(127, __float2int_rn(__fdiv_rn(e, l) * 127.f));
-            }
-            packed |= static_cast<uint32_t>(pv) << (8 * i);
-          }
-          w[q4] = packed;
-        }
-        // 16-byte chunk q of row r lives at chunk position q ^ (r % 8) (128-byte swizzle)
-        *reinterpret_cast<uint4*>(prow + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(prow + (((2 * c + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-      }
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(prow + (((4 * half + q) ^ sw) << 4)) =
+            make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
       fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(smem_u32(s_empty));
       mbar_arrive(smem_u32(p_full));
     }
-    // ---- epilogue: context rows
+    // ---- epilogue: context rows (each thread D/2 columns of its row)
     if (ok) ok = mbar_wait_status(smem_u32(o_full), 0, abort_flag, p.status, TI_ERR_ATT_O_FULL);
     if (ok) {
       tc_fence_after();
       int8_t* orow = p.ctx + static_cast<long long>(b) * p.ctx_batch_stride + static_cast<long long>(rg) * p.ld_ctx +
-                     h * D;
+                     h * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_o + lane_off + c * 32, v);
+      for (int c = 0; c < D / 64; ++c) {
+        tmem_ld_32x32(tmem_o + lane_off + half * (D / 2) + c * 32, va);
         tmem_ld_wait();
         uint32_t w[8];
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
-          uint32_t packed = 0;
+          int o[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float y = p.alpha_pv * __int2float_rn(static_cast<int>(v[q4 * 4 + i]));
-            const int o = max(-128, min(127, __float2int_rn(y)));
-            packed |= (static_cast<uint32_t>(o) & 0xFFu) << (8 * i);
-          }
-          w[q4] = packed;
+          for (int i = 0; i < 4; ++i)
+            o[i] = __float2int_rn(p.alpha_pv * __int2float_rn(static_cast<int>(va[q4 * 4 + i])));
+          w[q4] = pack_sat_s8x4(o[0], o[1], o[2], o[3]);
         }
         if (valid) {
           *reinterpret_cast<uint4*>(orow + c * 32) = make_uint4(w[0], w[1], w[2], w[3]);
