@@ -791,6 +791,31 @@ def run_reference(args, world, rank):
     print(json.dumps(line), flush=True)
 
 
+def profile_one_step(wl, region):
+    """One step of the OPT workload inside the CUDA profiler range (everything before it is warm-up)."""
+    model = wl.model
+    for _ in range(2):
+        wl.step()
+    if region == "prefill":
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        wl.step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    else:
+        cache = model.new_cache(wl.batch, wl.seq + 16)
+        out = model(wl.ids, past_key_values=cache, use_cache=True, last_token_only=True)
+        nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+        for _ in range(3):
+            nxt = model.decode_step(nxt, cache).argmax(dim=-1, keepdim=True)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        nxt = model.decode_step(nxt, cache).argmax(dim=-1, keepdim=True)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    print(json.dumps({"profiled": region, "workload": wl.name}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -806,6 +831,9 @@ def main():
                          "trace format) and add the per-stream busy times to the JSON line")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for ncu: no end-to-end leg, no CPU baseline")
+    ap.add_argument("--profile-region", default=None, choices=["prefill", "decode"],
+                    help="OPT workloads, one GPU: after warm-up, run ONE prefill step or ONE eager decode step between "
+                         "cudaProfilerStart/Stop and exit (for `ncu --profile-from-start off`: the launch list of a step)")
     args = ap.parse_args()
     world, rank, local = dist_env()
     key = pick_workload(args.workload, world)
@@ -843,6 +871,10 @@ def main():
     progress(f"workload {key} built, first step done")
     peaks = measured_peaks()
     from torch_int import _CUDA as C
+    if args.profile_region and key in OPT_WORKLOADS:
+        profile_one_step(wl, args.profile_region)
+        dog.disarm()
+        return
 
     def agreed_max(value):
         """Maximum of an integer over the ranks: every rank then takes the same decision."""

@@ -162,31 +162,43 @@ int ti_gemm_i8_ex(const ti_gemm_desc* desc, void* stream);
 /* Scratch bytes ti_gemm_desc.workspace must provide for an M x N output. */
 int64_t ti_split_k_workspace_bytes(int64_t M, int64_t N);
 
+/* Number of K splits the library chooses for an M x N x K problem that is given split-K scratch (a
+ * workspace in ti_gemm_desc, or the built-in array of ti_linear_a8_w8_b8_o8_static) on the current device:
+ * 1 means the scratch is not touched (M > 128, or N alone fills the SMs).  A query; launches nothing. */
+int ti_split_k_splits(int64_t M, int64_t N, int64_t K);
+
 /* ---- LayerNorm-quantise ops ---- */
 
 /* (residual_out, q) = dq_add_layernorm_q(input int32, input_scale, residual, gamma, beta, eps):
  *   residual_out = residual + input_scale * float(input)   (one fused multiply-add)
  *   q = int8(rne(clamp(LayerNorm(residual_out) * gamma + beta, -128, 127)))
  * rows x H row-major tensors; gamma, beta fp32 [H].  residual_is_half: 0 = fp32
- * residual / residual_out, 1 = fp16.
+ * residual / residual_out, 1 = fp16 (then, as torch::add and torch::layer_norm do for an fp16 tensor,
+ * the int32 input is converted to fp16 first and the LayerNorm output is rounded to fp16 before it is
+ * quantised; statistics are fp32).
  * Replaces dq_add_layernorm_q (torch_int/kernels/fused.cu:7-25), which issues
  * five ATen kernels. */
 int ti_dq_add_layernorm_q(const int32_t* input, float input_scale, const void* residual,
                           int residual_is_half, const float* gamma, const float* beta, float eps,
                           void* residual_out, int8_t* q, int64_t rows, int64_t H, void* stream);
 
-/* Same with an fp32 bias vector [H] applied to the dequantised input first:
- *   residual_out = residual + fma(input_scale, float(input), input_bias).
- * No reference counterpart: used when `input` is an int32 accumulator summed
- * across tensor-parallel ranks, so that the bias of the row-parallel linear
- * (torch_int/nn/linear.py:213-214) is added once, after the reduction. */
+/* The residual update of Int8OPTDecoderLayer with the preceding fp32-output linear folded in
+ * (torch_int/models/opt.py:281,289 after torch_int/nn/linear.py:213-214), then the next LayerNormQ:
+ *   d = fma(input_scale, float(input), input_bias)     the linear's fp32 output from its int32 accumulator
+ *   residual_out = residual + d                        fp32; with residual_is_half = 1, d is cast to fp16
+ *                                                      and added in fp16, as residual.add_(d.to(fp16)) does
+ *   q = int8(rne(clamp(LayerNorm(residual_out) * gamma + beta)))   in fp32 (LayerNormQ's fp32 parameters)
+ * No single reference counterpart; `input` may be an accumulator summed across tensor-parallel ranks,
+ * so that the bias of the row-parallel linear is added once, after the reduction. */
 int ti_dq_add_layernorm_q_bias(const int32_t* input, float input_scale, const float* input_bias,
                                const void* residual, int residual_is_half, const float* gamma,
                                const float* beta, float eps, void* residual_out, int8_t* q,
                                int64_t rows, int64_t H, void* stream);
 
-/* q = int8(clamp(rne(LayerNorm(x) * gamma + beta), -128, 127)); x fp32 (x_is_half=0)
- * or fp16 (1), gamma/beta fp32.
+/* q = int8(clamp(rne(LayerNorm(x) * gamma + beta), -128, 127)); gamma/beta fp32.  x_is_half: 0 = fp32 x;
+ * 2 = fp16 x normalised in fp32 (what LayerNormQ.forward computes with fp32 parameters: it casts x to
+ * their dtype first); 1 = fp16 x with the LayerNorm output rounded to fp16 before quantising (parameters
+ * cast to fp16 as well).
  * Replaces LayerNormQ.forward (torch_int/nn/fused.py:13-18), four ATen kernels. */
 int ti_layernorm_q(const void* x, int x_is_half, const float* gamma, const float* beta, float eps,
                    int8_t* q, int64_t rows, int64_t H, void* stream);

@@ -34,10 +34,11 @@ def _linear_f32(sd, prefix, x2d):
                                       _f(sd, prefix + ".a"), 1.0)
 
 
-def attention(sd, prefix, hidden_int8, mask, num_heads, past=None):
+def attention(sd, prefix, hidden_int8, mask, num_heads, past=None, trace=None):
     """Int8OPTAttention.forward (opt.py:83-199).  hidden_int8 [B,T,E] int8, mask
     additive [B,1,T,S] or None, past = (k, v) int8 [B,H,S0,D] or None.
-    Returns (fp32 [B,T,E], (k, v))."""
+    Returns (fp32 [B,T,E], (k, v)).  `trace`: optional dict that receives the int8 tensors between the
+    ops (q, k, v [B*H,*,D], probs [B*H,T,S], ctx [B,T,E])."""
     bsz, tgt, e = hidden_int8.shape
     d = e // num_heads
     x2d = hidden_int8.reshape(-1, e)
@@ -58,19 +59,28 @@ def attention(sd, prefix, hidden_int8, mask, num_heads, past=None):
     ctx = O.bmm_s8t_s8n_s8t(probs, v.transpose(1, 2).contiguous(), _f(sd, prefix + ".pv_bmm.a"))  # :180-181
     ctx = ctx.view(bsz, num_heads, tgt, d).transpose(1, 2).reshape(bsz, tgt, e).contiguous()      # :189-196
     out = _linear_f32(sd, prefix + ".out_proj", ctx.view(-1, e)).view(bsz, tgt, e)                 # :197
+    if trace is not None:
+        trace.update(q=q, k=k, v=v, probs=probs, ctx=ctx)
     return out, present
 
 
-def decoder_layer(sd, prefix, hidden, mask, num_heads, past=None, eps=1e-5):
-    """Int8OPTDecoderLayer.forward (opt.py:270-289): returns (residual, present kv)."""
+def decoder_layer(sd, prefix, hidden, mask, num_heads, past=None, eps=1e-5, trace=None):
+    """Int8OPTDecoderLayer.forward (opt.py:270-289): returns (residual, present kv).  `trace`: optional
+    dict that receives the tensors between the ops (ln1, q, k, v, probs, ctx, res1, ln2, fc1)."""
     residual = hidden.clone()
     h8 = O.layernorm_q(residual, sd[prefix + ".self_attn_layer_norm.weight"],
                        sd[prefix + ".self_attn_layer_norm.bias"], eps)
-    attn_out, present = attention(sd, prefix + ".self_attn", h8, mask, num_heads, past)
+    if trace is not None:
+        trace["ln1"] = h8
+    attn_out, present = attention(sd, prefix + ".self_attn", h8, mask, num_heads, past, trace)
     residual.add_(attn_out.to(residual.dtype))
     h8 = O.layernorm_q(residual, sd[prefix + ".final_layer_norm.weight"], sd[prefix + ".final_layer_norm.bias"], eps)
+    if trace is not None:
+        trace.update(res1=residual.clone(), ln2=h8)
     bsz, tgt, e = h8.shape
     h8 = _linear_s8(sd, prefix + ".fc1", h8.view(-1, e), relu=True)
+    if trace is not None:
+        trace["fc1"] = h8
     h = _linear_f32(sd, prefix + ".fc2", h8).view(bsz, tgt, e)
     residual.add_(h.to(residual.dtype))
     return residual, present

@@ -113,6 +113,18 @@ def linear_a8_w8_b8_o8(x, w, bias, alpha, beta, relu=False):
     return out
 
 
+def epilogue_s8_bias_s8(acc, bias, alpha, beta, relu=False):
+    """The int8 epilogue of linear_a8_w8_b8_o8 / linear_relu_a8_w8_b8_o8 applied to given int32
+    accumulators [M, N] (the C restatement; for callers that already hold the contraction)."""
+    acc = _c(acc, torch.int32)
+    m, n = acc.shape
+    b = _bias(bias, n, torch.int8)
+    out = torch.empty((m, n), dtype=torch.int8)
+    lib().ti_oracle_epi_s8_bias_s8(acc.data_ptr(), b.data_ptr(), out.data_ptr(), m, n,
+                                   float(alpha), float(beta), 1 if relu else 0)
+    return out
+
+
 def linear_relu_a8_w8_b8_o8(x, w, bias, alpha, beta):
     """linear_a8_w8_b8_o8 with max(y, 0) before rounding (linear.cu:476-625)."""
     return linear_a8_w8_b8_o8(x, w, bias, alpha, beta, relu=True)
@@ -237,8 +249,10 @@ def dq_add_layernorm_q_bias(input_int32, input_scale, input_bias, residual, gamm
     then LayerNormQ."""
     a = input_int32.numpy().astype(np.float32)
     d = _fma32(_f32(input_scale), a, np.broadcast_to(input_bias.numpy().astype(np.float32), a.shape))
-    r = residual + torch.from_numpy(d)
-    ln = torch.nn.functional.layer_norm(r, r.shape[-1:], gamma, beta, eps)
+    # residual.add_(d.to(residual.dtype)) of the decoder layer (models/opt.py:281,289), then LayerNormQ,
+    # which casts to its parameters' dtype first (nn/fused.py:14)
+    r = residual + torch.from_numpy(d).to(residual.dtype)
+    ln = torch.nn.functional.layer_norm(r.to(gamma.dtype), r.shape[-1:], gamma, beta, eps)
     return r, ln.clamp(-128, 127).round().to(torch.int8)
 
 

@@ -36,7 +36,10 @@ bmm_s8t_s8n_s8t = O.bmm_s8t_s8n_s8t
 bmm_s8t_s8n_f32t = O.bmm_s8t_s8n_f32t
 bmm_s8t_s8n_s32t = O.bmm_s8t_s8n_s32t
 dq_add_layernorm_q = O.dq_add_layernorm_q
-layernorm_q = O.layernorm_q
+
+
+def layernorm_q(x, gamma, beta, epsilon, fp32_norm=True):
+    return O.layernorm_q(x, gamma if fp32_norm else gamma.to(x.dtype), beta if fp32_norm else beta.to(x.dtype), epsilon)
 
 
 def dq_add_layernorm_q_bias(input, input_scale, input_bias, residual_input, gamma, beta, epsilon):

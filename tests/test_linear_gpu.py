@@ -121,6 +121,32 @@ def test_headline_gemm_full_tensor(cuda_ops):
     assert cuda_ops.device_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k,what", [
+    (4096, 7168, 7168, "OPT-30B q/k/v/out_proj, batch 8 x 512"),
+    (4096, 28672, 7168, "OPT-30B fc1"),
+    (4096, 7168, 28672, "OPT-30B fc2"),
+    (16384, 12288, 1536, "OPT-175B out_proj shard of one of 8 ranks, batch 16 x 1024"),
+    (16, 9216, 12288, "OPT-175B q/k/v shard of one of 4 ranks, decode step"),
+    (16, 12288, 3072, "OPT-175B out_proj shard of one of 4 ranks, decode step"),
+])
+def test_model_layer_shapes_full_tensor(cuda_ops, m, n, k, what):
+    """The GEMMs of the benchmarked models at their full per-layer (and per-rank) shapes, every element
+    against the oracle, in the epilogue the model uses there: int8 out with bias for the column-parallel
+    projections, raw int32 partial sums for the row-parallel ones."""
+    C = cuda_ops
+    x, w = rand_s8((m, k), 200 + m % 7), rand_s8((n, k), 201 + n % 7)
+    acc = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    C.gemm_i8_ex(x.cuda(), w.cuda(), acc, epilogue=C.EPI_S32_RAW, m=m, n=n, k=k, lda=k, ldb=k, ldc=n)
+    want = O.gemm_acc(x, w)
+    assert_bit_exact(acc, want, what + " (int32 partial sums)")
+    del acc
+    b8 = rand_s8((n,), 202)
+    alpha = 1.0 / (60.0 * k ** 0.5)
+    y = C.linear_relu_a8_w8_b8_o8(x.cuda(), w.cuda(), b8.cuda(), alpha, 0.05)
+    assert_bit_exact(y, O.epilogue_s8_bias_s8(want, b8, alpha, 0.05, relu=True), what + " (ReLU int8)")
+    assert C.device_status() == 0
+
+
 def test_linearity_property_at_full_size(cuda_ops):
     """Size-independent property: with int32 outputs, (x1 + x2) W^T == x1 W^T + x2 W^T."""
     C = cuda_ops

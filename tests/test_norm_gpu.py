@@ -90,6 +90,38 @@ def test_dq_add_layernorm_q_vs_reference_cpp(cuda_ops):
         assert_quant_close(q, q_ref, 0.999, f"q {shape}")
 
 
+def test_fp16_residual_paths(cuda_ops):
+    """The fp16 forms.  (1) dq_add_layernorm_q on an fp16 residual against the reference's own C++ op run on
+    fp16 CPU tensors (its torch::add converts the int32 input to fp16, its layer_norm returns fp16): residual
+    bit for bit, int8 within one unit at ties.  (2) The model's residual update with the linear folded in
+    (fp32 linear output cast to fp16, added in fp16, LayerNormQ in fp32) against the oracle.  (3) LayerNormQ
+    on an fp16 tensor with fp32 parameters (normalised in fp32) and with fp16 parameters."""
+    from oracle import build_ref
+    C = cuda_ops
+    shape, h = (3, 40, 5120), 5120
+    g = torch.Generator().manual_seed(31)
+    x = torch.randint(-30000, 30000, shape, generator=g, dtype=torch.int32)      # within fp16 range, as the op needs
+    res = randn(shape, 32).half()
+    gamma, beta = affine(h, 33, 30.0)
+    ref = build_ref.load()
+    if ref is not None:
+        r_ref, q_ref = ref.dq_add_layernorm_q(x, 2e-4, res, gamma, beta, 1e-5)
+        r, q = C.dq_add_layernorm_q(x.cuda(), 2e-4, res.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+        assert r.dtype == torch.float16 and torch.equal(r.cpu(), r_ref), "fp16 residual output"
+        assert_quant_close(q, q_ref, 0.999, "fp16 dq_add_layernorm_q vs the reference's C++ op")
+    big = torch.randint(-2000000, 2000000, shape, generator=g, dtype=torch.int32)  # accumulator-sized values
+    bias = randn((h,), 34, 0.5)
+    r, q = C.dq_add_layernorm_q_bias(big.cuda(), 3e-6, bias.cuda(), res.cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+    r_o, q_o = O.dq_add_layernorm_q_bias(big, 3e-6, bias, res, gamma, beta, 1e-5)
+    assert r.dtype == torch.float16 and torch.equal(r.cpu(), r_o), "model residual update in fp16"
+    assert_quant_close(q, q_o, 0.999, "LayerNormQ after the fp16 residual update")
+    xh = randn(shape, 35, 3.0).half()
+    assert_quant_close(C.layernorm_q(xh.cuda(), gamma.cuda(), beta.cuda(), 1e-5), O.layernorm_q(xh, gamma, beta, 1e-5),
+                       0.999, "fp16 input, fp32 LayerNorm")
+    assert_quant_close(C.layernorm_q(xh.cuda(), gamma.cuda(), beta.cuda(), 1e-5, fp32_norm=False),
+                       O.layernorm_q(xh, gamma.half(), beta.half(), 1e-5), 0.995, "fp16 input and parameters")
+
+
 def test_dq_add_module(cuda_ops):
     from torch_int.nn.fused import DQ_Add_LayerNorm_Q
     m = DQ_Add_LayerNorm_Q(256).cuda()

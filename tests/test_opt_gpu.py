@@ -101,6 +101,84 @@ def test_decoder_layer_opt13b_dims(cuda_ops):
     assert cuda_ops.device_status() == 0
 
 
+def _stagewise_layer_check(C, model, hidden, heads, what):
+    """Every op of one decoder layer, fed with the ORACLE's tensor of the previous stage, against the
+    oracle's tensor of this stage: integer GEMM stages bit for bit, LayerNorm / softmax stages within one
+    unit at rounding ties (>= 99.9 % identical), fp32 residuals bit for bit.  A wrong scale, bias or head
+    offset anywhere in the layer's wiring fails its stage outright.  Then the layer as a whole."""
+    from helpers import assert_quant_close
+    layer = model.model.decoder.layers[0]
+    attn = layer.self_attn
+    sd = cpu_sd(model)
+    bsz, seq, e = hidden.shape
+    d = e // heads
+    mask = O.causal_mask(bsz, seq, seq)
+    tr = {}
+    want, _ = OM.decoder_layer(sd, "model.decoder.layers.0", hidden, mask, heads, trace=tr)
+    ln1, ln2 = layer.self_attn_layer_norm, layer.final_layer_norm
+    assert_quant_close(C.layernorm_q(hidden.cuda(), ln1.weight, ln1.bias, ln1.eps), tr["ln1"], what=what + " ln1")
+    x = tr["ln1"].cuda()
+
+    def heads_first(t):                       # [B,T,E] -> [B*H,T,D]
+        return t.view(bsz, seq, heads, d).transpose(1, 2).reshape(bsz * heads, seq, d).contiguous()
+    for name, proj in (("q", attn.q_proj), ("k", attn.k_proj), ("v", attn.v_proj)):
+        assert_bit_exact(heads_first(proj(x)), tr[name], f"{what} {name}_proj")
+    q, k, v = tr["q"].cuda(), tr["k"].cuda(), tr["v"].cuda()
+    probs = C.softmax_q(attn.qk_bmm(q, k), None, heads, causal=0)
+    assert_quant_close(probs, tr["probs"], what=what + " probabilities")
+    ctx3 = attn.pv_bmm(tr["probs"].cuda(), v.transpose(1, 2).contiguous())
+    ctx3 = ctx3.view(bsz, heads, seq, d).transpose(1, 2).reshape(bsz, seq, e)
+    assert_bit_exact(ctx3, tr["ctx"], what + " context (P.V)")
+    # the one-kernel attention on the oracle's q, k, v: a probability that flips at a tie moves a context
+    # value by at most alpha_pv * 127
+    rows = lambda t: t.view(bsz, heads, seq, d).transpose(1, 2).reshape(bsz, seq, e).contiguous()  # noqa: E731
+    out = torch.empty((bsz, seq, e), dtype=torch.int8, device="cuda")
+    C.attention_prefill(rows(q), rows(k), v.view(bsz, heads, seq, d).transpose(2, 3).contiguous(), out, batch=bsz,
+                        heads=heads, head_dim=d, tgt_len=seq, src_len=seq, ld_q=e, q_batch_stride=seq * e, ld_k=e,
+                        k_batch_stride=seq * e, ld_vt=seq, alpha_qk=attn.qk_bmm._alpha(), alpha_pv=attn.pv_bmm._alpha())
+    dctx = (out.cpu().int() - tr["ctx"].int()).abs()
+    assert float((dctx == 0).double().mean()) >= 0.995, what + " fused attention context"
+    assert int(dctx.max()) <= int(abs(attn.pv_bmm._alpha()) * 127) + 1
+    # out_proj as int32 partial sums + scale + bias + residual add + LayerNorm-quantise
+    acc = torch.empty((bsz * seq, e), dtype=torch.int32, device="cuda")
+    C.gemm_i8_ex(tr["ctx"].cuda().view(-1, e), attn.out_proj.weight, acc, epilogue=C.EPI_S32_RAW, m=bsz * seq, n=e,
+                 k=e, lda=e, ldb=e, ldc=e)
+    res1, h8 = C.dq_add_layernorm_q_bias(acc.view(bsz, seq, e), attn.out_proj._scalar("a"), attn.out_proj.bias,
+                                         hidden.cuda(), ln2.weight, ln2.bias, ln2.eps)
+    assert_bit_exact(res1.view(torch.int32), tr["res1"].view(torch.int32), what + " residual after attention")
+    assert_quant_close(h8, tr["ln2"], what=what + " ln2")
+    f8 = layer.fc1(tr["ln2"].cuda().view(-1, e))
+    assert_bit_exact(f8, tr["fc1"], what + " fc1")
+    C.gemm_i8_ex(f8, layer.fc2.weight, acc, epilogue=C.EPI_S32_RAW, m=bsz * seq, n=e, k=f8.shape[1],
+                 lda=f8.shape[1], ldb=f8.shape[1], ldc=e)
+    ident = layer._identity_ln(torch.device("cuda"))
+    res2, _ = C.dq_add_layernorm_q_bias(acc.view(bsz, seq, e), layer.fc2._scalar("a"), layer.fc2.bias,
+                                        tr["res1"].cuda(), ident.weight, ident.bias, ident.eps)
+    # fed with the oracle's fc1 output and residual, the layer's output is the oracle's bit for bit
+    assert_bit_exact(res2.view(torch.int32), want.view(torch.int32), what + " layer output (stage-wise)")
+    # ... and the layer as a whole (tie flips of earlier stages propagate: a relative bound)
+    whole = layer(hidden.cuda().clone(), attention_mask=mask.cuda())[0]
+    assert rel_err(whole, want) < 1e-2
+    assert C.device_status() == 0
+
+
+def test_layer_stagewise_opt13b_batch4(cuda_ops):
+    """Int8OPTDecoderLayer at the OPT-13B dimensions (hidden 5120, 40 heads, FFN 20480), batch 4 x 512."""
+    cfg, model = small_model(layers=1, hidden=5120, heads=40, ffn=20480, vocab=64)
+    _stagewise_layer_check(cuda_ops, model, randn((4, 512, 5120), 16), 40, "OPT-13B layer")
+
+
+def test_layer_stagewise_opt30b(cuda_ops):
+    """One layer at the OPT-30B dimensions (hidden 7168, 56 heads, FFN 28672), 1 x 512 tokens."""
+    cfg, model = small_model(layers=1, hidden=7168, heads=56, ffn=28672, vocab=64)
+    _stagewise_layer_check(cuda_ops, model, randn((1, 512, 7168), 17), 56, "OPT-30B layer")
+
+
+def test_layer_stagewise_small(cuda_ops):
+    cfg, model = small_model(layers=1, hidden=512, heads=4, ffn=2048)
+    _stagewise_layer_check(cuda_ops, model, randn((2, 192, 512), 18), 4, "small layer")
+
+
 @pytest.mark.parametrize("seq", [64, 255])
 def test_causal_lm_logits(cuda_ops, seq):
     # L = 255 exercises a sequence length that is not a multiple of 16, as the
@@ -121,6 +199,60 @@ def test_causal_lm_logits(cuda_ops, seq):
         unfused = model(ids.cuda()).logits
         assert_bit_exact(ref_path.view(torch.int32), unfused.view(torch.int32), "reference-signature layers vs fused wiring")
         assert rel_err(unfused, logits) < 1e-2   # one-kernel attention: tie flips only
+
+
+def test_fp16_residual_stream(cuda_ops):
+    """A model held in fp16 (the reference benchmark's default precision, int8-fp16): with residual_dtype =
+    None the fused wiring keeps the residual stream in fp16 exactly as the reference-signature layers do
+    (bit-identical logits with the same attention kernels), and agrees with the oracle's fp16 evaluation."""
+    from torch_int.models.opt import Int8OPTConfig
+    from torch_int.models.random_init import random_int8_opt
+    cfg = Int8OPTConfig(vocab_size=512, hidden_size=256, num_hidden_layers=3, ffn_dim=1024, num_attention_heads=4,
+                        max_position_embeddings=512)
+    model = random_int8_opt(cfg, seed=4, device="cuda", param_dtype=torch.float16)
+    sd = cpu_sd(model)
+    ids = torch.randint(0, cfg.vocab_size, (2, 64), generator=torch.Generator().manual_seed(3))
+    dec = model.model.decoder
+    assert dec.residual_dtype == torch.float32
+    fp32_stream = model(ids.cuda()).logits
+    dec.residual_dtype = None                      # follow the embeddings, as the reference does
+    set_fused_attention(model, False)
+    got = model(ids.cuda()).logits
+    ref_path = model(ids.cuda(), reference_path=True).logits
+    assert got.dtype == torch.float16
+    assert_bit_exact(got.view(torch.int16), ref_path.view(torch.int16), "fp16 residual: fused vs reference wiring")
+    want, _ = OM.causal_lm_logits(sd, cfg, ids)    # fp16 embeddings -> the oracle's residual stream is fp16 too
+    assert want.dtype == torch.float16 and rel_err(got, want) < 2e-2
+    assert rel_err(got, fp32_stream) < 2e-2 and not torch.equal(got, fp32_stream)
+    # decode steps on the fp16 stream reproduce the full forward
+    set_fused_attention(model, True)
+    out = model.generate_greedy(ids[:, :20].cuda(), 5)
+    full = model(out[:, :-1]).logits
+    assert torch.equal(full[:, 19:, :].argmax(-1), out[:, 20:])
+    assert cuda_ops.device_status() == 0
+
+
+@pytest.mark.parametrize("safe,dtype", [(True, torch.float32), (False, torch.float16)])
+def test_checkpoint_round_trip_on_the_gpu(cuda_ops, tmp_path, safe, dtype):
+    """save_pretrained -> from_pretrained(device="cuda") (the reference's inherited pair,
+    benchmark/bench_opt.py:35-40): the reloaded model gives bit-identical logits and tokens."""
+    from torch_int.models.opt import Int8OPTConfig, Int8OPTForCausalLM, Int8OPTModel
+    from torch_int.models.random_init import random_int8_opt
+    cfg = Int8OPTConfig(vocab_size=512, hidden_size=256, num_hidden_layers=3, ffn_dim=1024, num_attention_heads=4,
+                        max_position_embeddings=256)
+    model = random_int8_opt(cfg, seed=12, device="cuda", param_dtype=dtype)
+    ids = torch.randint(0, cfg.vocab_size, (2, 77), generator=torch.Generator().manual_seed(2)).cuda()
+    want = model(ids).logits
+    model.save_pretrained(str(tmp_path), max_shard_bytes=300000, safe_serialization=safe)   # several files
+    again = Int8OPTForCausalLM.from_pretrained(str(tmp_path), device="cuda")
+    assert next(again.parameters()).is_cuda and again.model.decoder.embed_tokens.weight.dtype == dtype
+    assert_bit_exact(again(ids).logits.view(torch.int32 if dtype == torch.float32 else torch.int16),
+                     want.view(torch.int32 if dtype == torch.float32 else torch.int16), "reloaded model")
+    assert torch.equal(again.generate_greedy(ids[:, :30], 6), model.generate_greedy(ids[:, :30], 6))
+    # the decoder-only class reads the same directory (keys with the "model." prefix)
+    body = Int8OPTModel.from_pretrained(str(tmp_path), device="cuda")
+    assert torch.equal(body(ids).last_hidden_state, model.model(ids).last_hidden_state)
+    assert cuda_ops.device_status() == 0
 
 
 def test_padding_mask(cuda_ops):
@@ -185,10 +317,54 @@ def test_decode_attention_kernel(cuda_ops, bsz, heads, d, length):
     probs = O.softmax_q(O.bmm_s8t_s8n_f32t(q, k, a_qk))
     vt = vals[..., :s].reshape(bsz * heads, d, s).contiguous()
     want = O.bmm_s8t_s8n_s8t(probs, vt, a_pv).view(bsz, heads * d)
+    # a probability that flips at a rounding tie moves a context value by up to alpha_pv * 127 = 2.5
     diff = (ctx.cpu().int() - want.int()).abs()
-    assert int(diff.max()) <= 2 and float((diff == 0).double().mean()) > 0.97, (int(diff.max()), float((diff == 0).double().mean()))
+    assert int(diff.max()) <= 3 and float((diff == 0).double().mean()) >= 0.999, \
+        (int(diff.max()), float((diff == 0).double().mean()))
     C.advance_position(pos, 1)
     assert int(pos.item()) == length + 1
+    assert C.device_status() == 0
+
+
+@pytest.mark.parametrize("bsz,heads,d,length", [(2, 2, 128, 127), (1, 3, 64, 500), (2, 1, 128, 1023)])
+def test_decode_attention_probabilities(cuda_ops, bsz, heads, d, length):
+    """The probabilities inside the one-token attention kernel, made visible: with alpha_pv = 1 and a value
+    matrix that holds a single 1 per row (row r of head h selects position sel[h][r]), the context IS the
+    int8 probability of the selected positions.  They obey the common rule of the softmax paths: at most
+    one unit from the oracle, at least 99.9 % identical."""
+    from helpers import assert_quant_close
+    C = cuda_ops
+    e, cap = heads * d, 1024
+    s = length + 1
+    g = torch.Generator().manual_seed(23)
+    keys = torch.randint(-127, 128, (bsz, cap, e), generator=g, dtype=torch.int8)
+    qkv = torch.randint(-60, 61, (bsz + 16, 3 * e), generator=g, dtype=torch.int8)
+    a_qk = 1.5 / (35.0 * 73.0 * d ** 0.5)
+    # the probabilities do not depend on the values: evaluate the oracle once
+    kk = keys.clone()
+    kk[:, length] = qkv[:bsz, e:2 * e]
+    qh = qkv[:bsz, :e].view(bsz, 1, heads, d).transpose(1, 2).reshape(bsz * heads, 1, d).contiguous()
+    kh = kk[:, :s].view(bsz, s, heads, d).transpose(1, 2).reshape(bsz * heads, s, d).contiguous()
+    probs = O.softmax_q(O.bmm_s8t_s8n_f32t(qh, kh, a_qk)).view(bsz, heads, s)
+    got, want = [], []
+    for rep in range(4):                                  # different selections: 4 * d positions per head
+        if rep == 0:    # the positions with the largest probabilities (of the first sequence), then random ones
+            sel = torch.stack([probs[0, h].int().argsort(descending=True)[torch.arange(d) % s] for h in range(heads)])
+        else:
+            sel = torch.stack([torch.randperm(s, generator=g)[torch.arange(d) % s] for _ in range(heads)])
+        vals = torch.zeros((bsz, heads, d, cap), dtype=torch.int8)
+        for h in range(heads):
+            vals[:, h, torch.arange(d), sel[h]] = 1
+        # the kernel appends v of the new token at column `length`: make that column consistent with `vals`
+        q3 = qkv.clone()
+        q3[:bsz, 2 * e:] = vals[..., length].reshape(bsz, e)
+        pos = torch.full((1,), length, dtype=torch.int32, device="cuda")
+        ctx = C.decode_attention(q3.cuda(), keys.cuda(), vals.cuda(), pos, a_qk, 1.0).cpu().view(bsz, heads, d)
+        got.append(ctx)
+        want.append(torch.stack([probs[:, h, sel[h]] for h in range(heads)], dim=1))
+    got, want = torch.cat(got), torch.cat(want)
+    assert_quant_close(got, want, 0.999, "decode attention probabilities")
+    assert int(want.int().abs().max()) >= 2               # the selection sees non-zero probabilities
     assert C.device_status() == 0
 
 

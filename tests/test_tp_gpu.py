@@ -54,6 +54,33 @@ def _rank_main(rank, world, port, ret, big):
         again = tp_model(ids4).logits                       # a second pass over the same workspace
         gen = tp_model.generate_greedy(ids4[:, :prompt], new)   # static cache, one-token steps
         tp = tp_model.model.decoder.tp
+        extra_ok = True
+        if not big:
+            # checkpoint round trip under tensor parallelism: rank 0 writes the whole model, every rank
+            # reads only its slices of it, and the logits stay bit-identical
+            import tempfile
+            from torch_int.models.opt import Int8OPTForCausalLM
+            box = [tempfile.mkdtemp(prefix="ti_ckpt_") if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            if rank == 0:
+                random_int8_opt(cfg, seed=21, device=dev, tp=TensorParallel.single(), consistent=True).save_pretrained(box[0])
+            dist.barrier()
+            loaded = Int8OPTForCausalLM.from_pretrained(box[0], device=dev, tp=TensorParallel.from_world())
+            loaded.model.decoder.tp.min_pipeline_tokens = 32
+            extra_ok = extra_ok and torch.equal(loaded(ids4).logits, logits4)
+            # vocabulary-parallel language-model head: each rank multiplies with its rows of the tied table
+            vp = loaded.model.decoder.tp
+            vp.vocab_parallel = True
+            split = loaded(ids4).logits
+            vp.vocab_parallel = False
+            scale = float(logits4.abs().max())
+            extra_ok = extra_ok and split.shape == logits4.shape and float((split - logits4).abs().max()) <= 1e-4 * scale
+            extra_ok = extra_ok and torch.equal(split.argmax(-1), logits4.argmax(-1))
+            del loaded
+            dist.barrier()
+            if rank == 0:
+                import shutil
+                shutil.rmtree(box[0], ignore_errors=True)
         peer = tp.use_peer_memory and len(tp._workspaces) > 0  # the fused peer-memory exchange really ran
         checked = all(ws.checked for ws in tp._workspaces.values())
         status = C.device_status()
@@ -64,7 +91,7 @@ def _rank_main(rank, world, port, ret, big):
             one = random_int8_opt(cfg, seed=21, device=dev, tp=TensorParallel.single(), consistent=True)
             ok = (torch.equal(logits, one(ids).logits) and torch.equal(logits4, one(ids4).logits)
                   and torch.equal(again, logits4) and torch.equal(gen, one.generate_greedy(ids4[:, :prompt], new)))
-        ret[rank] = (bool(ok and peer and checked), status)
+        ret[rank] = (bool(ok and peer and checked and extra_ok), status)
     finally:
         dist.destroy_process_group()
 

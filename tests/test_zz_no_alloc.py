@@ -28,6 +28,8 @@ def _lib():
         fn.restype = ctypes.c_int
     lib.ti_last_error.restype = ctypes.c_char_p
     lib.ti_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+    lib.ti_split_k_splits.argtypes = [i64, i64, i64]
+    lib.ti_split_k_splits.restype = ctypes.c_int
     return lib
 
 
@@ -55,6 +57,12 @@ def test_static_scratch_entry_point_matches_regular_one_twice():
         assert rc == 0, lib.ti_last_error()
         torch.cuda.synchronize()
         assert torch.equal(got, want), f"call {call}: {int((got != want).sum())} of {got.numel()} int8 outputs differ"
+        # the call really went through the built-in scratch (K split over several CTAs), and both entry
+        # points give what the CPU oracle gives
+        assert lib.ti_split_k_splits(m, n, k) > 1, "this problem is expected to take the split-K path"
+        from oracle import w8a8 as O
+        assert torch.equal(got.cpu(), O.linear_a8_w8_b8_o8(x.cpu(), w.cpu(), b.cpu(), alpha, beta)), \
+            f"call {call}: differs from the oracle"
     status = ctypes.c_int(-1)
     assert lib.ti_device_status(ctypes.byref(status), 1) == 0 and status.value == 0
 

@@ -302,6 +302,8 @@ int ti_tp_barrier(void* const* pads, int32_t rank, int32_t n, uint32_t epoch, vo
 
 int64_t ti_split_k_workspace_bytes(int64_t M, int64_t N) { return split_k_workspace_bytes(M, N); }
 
+int ti_split_k_splits(int64_t M, int64_t N, int64_t K) { return split_k_auto_splits(M, N, K); }
+
 int ti_set_sm_limit(int sms) {
   set_sm_limit(sms);
   return TI_OK;

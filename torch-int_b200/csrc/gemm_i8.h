@@ -59,6 +59,10 @@ int launch_gemm_i8(const GemmProblem& p, cudaStream_t stream);
 // Bytes of split-K workspace a problem with M rows and N columns needs.
 int64_t split_k_workspace_bytes(int64_t M, int64_t N);
 
+// K splits the automatic choice makes for an M x N x K problem that is given a workspace (1 = no split:
+// M > 128, or enough N tiles to fill the SMs).
+int split_k_auto_splits(int64_t M, int64_t N, int64_t K);
+
 // Caps the number of SMs the persistent GEMM grids use (0 = all SMs of the device).
 void set_sm_limit(int sms);
 

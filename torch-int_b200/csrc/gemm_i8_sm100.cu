@@ -792,7 +792,41 @@ void choose_tile(const GemmProblem& g, int* bn_out, bool* pair_out) {
   *pair_out = best_pair;
 }
 
+// Number of K splits for a small-M problem with N tile `bn_split` (1 = none).  `wanted` > 1 asks for
+// that many (capped so that a split keeps at least 8 K blocks); 0 chooses: the cost, in K blocks, is
+// (rounds of the persistent grid) x (K blocks per work item + a charge for the workspace reduction and
+// the last-CTA epilogue).
+int choose_splits(int64_t N, int64_t K, int bn_split, int wanted) {
+  const long long num_kb = (K + BK - 1) / BK;
+  const long long tiles = (N + bn_split - 1) / bn_split;
+  const long long sms = num_sms();
+  long long max_splits = num_kb / 8 > 0 ? num_kb / 8 : 1;
+  if (max_splits > 64) max_splits = 64;
+  int splits = 1;
+  if (wanted > 1) {
+    splits = static_cast<int>(wanted < max_splits ? wanted : max_splits);
+  } else if (tiles < sms) {
+    long long best_cost = num_kb * ((tiles + sms - 1) / sms);
+    for (long long sp = 2; sp <= max_splits; ++sp) {
+      const long long per = (num_kb + sp - 1) / sp;
+      const long long eff = (num_kb + per - 1) / per;
+      const long long rounds = (tiles * eff + sms - 1) / sms;
+      const long long cost = rounds * (per + 6);
+      if (cost < best_cost) {
+        best_cost = cost;
+        splits = static_cast<int>(eff);
+      }
+    }
+  }
+  return splits;
+}
+
 }  // namespace
+
+int split_k_auto_splits(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || M > BM || N <= 0 || K <= 0) return 1;
+  return choose_splits(N, K, N >= 4096 ? 128 : 64, 0);
+}
 
 int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
   if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0 || g.batch2 < 0) {
@@ -887,29 +921,8 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
       set_error("split-K workspace must be 256-byte aligned");
       return TI_E_INVALID;
     }
-    const long long num_kb = (g.K + BK - 1) / BK;
     const int bn_split = g.force_bn ? bn : (g.N >= 4096 ? 128 : 64);
-    const long long tiles = (g.N + bn_split - 1) / bn_split;
-    const long long sms = num_sms();
-    long long max_splits = num_kb / 8 > 0 ? num_kb / 8 : 1;  // at least 8 K blocks per split
-    if (max_splits > 64) max_splits = 64;
-    if (g.splits > 1) {
-      splits = static_cast<int>(g.splits < max_splits ? g.splits : max_splits);
-    } else if (tiles < sms) {
-      // cost in K blocks: (rounds of the persistent grid) x (K blocks per work item), plus a
-      // per-work-item charge for the workspace reduction and the last-CTA epilogue
-      long long best_cost = num_kb * ((tiles + sms - 1) / sms) ;
-      for (long long sp = 2; sp <= max_splits; ++sp) {
-        const long long per = (num_kb + sp - 1) / sp;
-        const long long eff = (num_kb + per - 1) / per;
-        const long long rounds = (tiles * eff + sms - 1) / sms;
-        const long long cost = rounds * (per + 6);
-        if (cost < best_cost) {
-          best_cost = cost;
-          splits = static_cast<int>(eff);
-        }
-      }
-    }
+    splits = choose_splits(g.N, g.K, bn_split, g.splits);
     if (splits > 1) bn = bn_split;  // otherwise keep the tile the general chooser picked
   }
   switch (g.epilogue) {

@@ -138,7 +138,10 @@ __device__ __forceinline__ void layernorm_quant_row(float4 (&x)[VPT], int h4, co
   }
 }
 
-template <typename T, int THREADS, int VPT>
+// T: storage type of x.  LN: float = the LayerNorm output stays fp32 (the reference's LayerNormQ with
+// fp32 parameters casts x to fp32 first, nn/fused.py:14); __half = it is rounded to fp16 before
+// quantising (parameters cast to fp16 as well).
+template <typename T, typename LN, int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 layernorm_q_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                    const float* __restrict__ beta, float eps, int8_t* __restrict__ q, int H,
@@ -153,7 +156,7 @@ layernorm_q_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
     const int i = threadIdx.x + j * THREADS;
     if (i < h4) v[j] = load4<T>(xr + 4 * i);
   }
-  layernorm_quant_row<T, THREADS, VPT>(v, h4, gamma, beta, eps, H, q + row * ldq, scratch);
+  layernorm_quant_row<LN, THREADS, VPT>(v, h4, gamma, beta, eps, H, q + row * ldq, scratch);
 }
 
 template <typename T, int THREADS, int VPT>
@@ -179,15 +182,15 @@ dq_add_layernorm_q_kernel(const int32_t* __restrict__ in, float scale, const T* 
                              round_to_storage<T>(__int2float_rn(a.z)), round_to_storage<T>(__int2float_rn(a.w)));
       float4 o;
       if (in_bias != nullptr) {
-        // Extension for the row-parallel tensor-parallel path: the int32 input is
-        // an all-reduced accumulator, so the linear layer's fp32 bias is applied
-        // here: d = fma(scale, acc, bias) as the fp32-output linear does, then
-        // the residual add.
+        // The model's residual update with the linear layer folded in: the int32 input is the
+        // accumulator of an fp32-output linear (W8A8BFP32OFP32Linear), so d = fma(scale, float(acc),
+        // bias) in fp32 exactly as that linear computes it, d is cast to the residual's dtype and
+        // added there (models/opt.py:281,289: residual.add_(hidden_states.to(residual.dtype))).
         const float4 bb = *reinterpret_cast<const float4*>(in_bias + 4 * i);
-        o.x = r.x + __fmaf_rn(scale, f.x, bb.x);
-        o.y = r.y + __fmaf_rn(scale, f.y, bb.y);
-        o.z = r.z + __fmaf_rn(scale, f.z, bb.z);
-        o.w = r.w + __fmaf_rn(scale, f.w, bb.w);
+        o.x = r.x + round_to_storage<T>(__fmaf_rn(scale, __int2float_rn(a.x), bb.x));
+        o.y = r.y + round_to_storage<T>(__fmaf_rn(scale, __int2float_rn(a.y), bb.y));
+        o.z = r.z + round_to_storage<T>(__fmaf_rn(scale, __int2float_rn(a.z), bb.z));
+        o.w = r.w + round_to_storage<T>(__fmaf_rn(scale, __int2float_rn(a.w), bb.w));
       } else {
         o.x = __fmaf_rn(scale, f.x, r.x);
         o.y = __fmaf_rn(scale, f.y, r.y);
@@ -202,14 +205,19 @@ dq_add_layernorm_q_kernel(const int32_t* __restrict__ in, float scale, const T* 
       v[j] = o;
     }
   }
-  layernorm_quant_row<T, THREADS, VPT>(v, h4, gamma, beta, eps, H, q + row * static_cast<long long>(H),
-                                       scratch);
+  // with a bias this is the model path: the next LayerNormQ has fp32 parameters and normalises in fp32
+  if (in_bias != nullptr)
+    layernorm_quant_row<float, THREADS, VPT>(v, h4, gamma, beta, eps, H, q + row * static_cast<long long>(H),
+                                             scratch);
+  else
+    layernorm_quant_row<T, THREADS, VPT>(v, h4, gamma, beta, eps, H, q + row * static_cast<long long>(H),
+                                         scratch);
 }
 
 // Scalar, multi-pass fallback for row lengths the register-resident kernels do
 // not cover (H not a multiple of 4, or H > 256 * 4 * kMaxVpt).  Rows are read
 // three times; the second and third reads hit L1/L2.
-template <typename T, bool kDq>
+template <typename T, typename LN, bool kDq>
 __global__ void __launch_bounds__(256)
 layernorm_q_generic_kernel(const T* __restrict__ x, const int32_t* __restrict__ in, float scale,
                            const float* __restrict__ in_bias, const float* __restrict__ gamma,
@@ -221,11 +229,10 @@ layernorm_q_generic_kernel(const T* __restrict__ x, const int32_t* __restrict__ 
   auto value = [&](int i) -> float {
     float r = static_cast<float>(xr[i]);
     if constexpr (kDq) {
-      const float f = round_to_storage<T>(__int2float_rn(in[row * H + i]));
-      if (in_bias != nullptr)
-        r = r + __fmaf_rn(scale, f, in_bias[i]);
+      if (in_bias != nullptr)  // model path: fp32 linear output cast to the residual's dtype, then added
+        r = r + round_to_storage<T>(__fmaf_rn(scale, __int2float_rn(in[row * H + i]), in_bias[i]));
       else
-        r = __fmaf_rn(scale, f, r);
+        r = __fmaf_rn(scale, round_to_storage<T>(__int2float_rn(in[row * H + i])), r);
       r = round_to_storage<T>(r);
     }
     return r;
@@ -245,7 +252,9 @@ layernorm_q_generic_kernel(const T* __restrict__ x, const int32_t* __restrict__ 
   const float var = block_reduce<256, false>(ss, scratch) / static_cast<float>(H);
   const float rstd = __fdiv_rn(1.f, __fsqrt_rn(var + eps));
   for (int i = threadIdx.x; i < H; i += 256) {
-    const float y = round_to_storage<T>(__fmaf_rn((value(i) - mean) * rstd, gamma[i], beta[i]));
+    float y = __fmaf_rn((value(i) - mean) * rstd, gamma[i], beta[i]);
+    // the model path (a bias is given) normalises in fp32 like LayerNormQ with fp32 parameters
+    y = (kDq && in_bias != nullptr) ? y : round_to_storage<LN>(y);
     q[row * ldq + i] = static_cast<int8_t>(quant_s8(y));
   }
 }
@@ -711,7 +720,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
     default: { constexpr int VPT = 16; __VA_ARGS__; break; }          \
   }
 
-template <typename T>
+template <typename T, typename LN>
 int layernorm_q_typed(const T* x, const float* gamma, const float* beta, float eps, int8_t* q,
                       int64_t rows, int64_t H, cudaStream_t stream) {
   const int h4 = static_cast<int>(H / 4);
@@ -720,18 +729,18 @@ int layernorm_q_typed(const T* x, const float* gamma, const float* beta, float e
   const unsigned grid = static_cast<unsigned>(rows);
   if (!fast)
     return check_launch("layernorm_q_generic", [&] {
-      layernorm_q_generic_kernel<T, false><<<grid, 256, 0, stream>>>(
+      layernorm_q_generic_kernel<T, LN, false><<<grid, 256, 0, stream>>>(
           x, nullptr, 0.f, nullptr, gamma, beta, eps, nullptr, q, static_cast<int>(H), H, H);
     });
   if (h4 <= 128)
     return check_launch("layernorm_q", [&] {
-      layernorm_q_kernel<T, 128, 1><<<grid, 128, 0, stream>>>(x, gamma, beta, eps, q,
-                                                              static_cast<int>(H), H, H);
+      layernorm_q_kernel<T, LN, 128, 1><<<grid, 128, 0, stream>>>(x, gamma, beta, eps, q,
+                                                                  static_cast<int>(H), H, H);
     });
   const int vpt = (h4 + 255) / 256;
   int rc = TI_OK;
   TI_VPT_SWITCH(vpt, rc = check_launch("layernorm_q", [&] {
-                  layernorm_q_kernel<T, 256, VPT><<<grid, 256, 0, stream>>>(
+                  layernorm_q_kernel<T, LN, 256, VPT><<<grid, 256, 0, stream>>>(
                       x, gamma, beta, eps, q, static_cast<int>(H), H, H);
                 }));
   return rc;
@@ -749,7 +758,7 @@ int dq_add_layernorm_q_typed(const int32_t* in, float scale, const T* res, const
   const unsigned grid = static_cast<unsigned>(rows);
   if (!fast)
     return check_launch("dq_add_layernorm_q_generic", [&] {
-      layernorm_q_generic_kernel<T, true><<<grid, 256, 0, stream>>>(
+      layernorm_q_generic_kernel<T, T, true><<<grid, 256, 0, stream>>>(
           res, in, scale, in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H), H, H);
     });
   if (h4 <= 128)
@@ -783,9 +792,11 @@ int layernorm_q(const void* x, int x_is_half, const float* gamma, const float* b
     set_error("layernorm_q: too many rows");
     return TI_E_INVALID;
   }
+  if (x_is_half == 2)  // fp16 input, fp32 LayerNorm (LayerNormQ with fp32 parameters)
+    return layernorm_q_typed<__half, float>(static_cast<const __half*>(x), gamma, beta, eps, q, rows, H, stream);
   if (x_is_half)
-    return layernorm_q_typed<__half>(static_cast<const __half*>(x), gamma, beta, eps, q, rows, H, stream);
-  return layernorm_q_typed<float>(static_cast<const float*>(x), gamma, beta, eps, q, rows, H, stream);
+    return layernorm_q_typed<__half, __half>(static_cast<const __half*>(x), gamma, beta, eps, q, rows, H, stream);
+  return layernorm_q_typed<float, float>(static_cast<const float*>(x), gamma, beta, eps, q, rows, H, stream);
 }
 
 int dq_add_layernorm_q(const int32_t* in, float scale, const void* res, int res_is_half,

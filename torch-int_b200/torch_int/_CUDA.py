@@ -360,11 +360,15 @@ def dq_add_layernorm_q_bias(input, input_scale, input_bias, residual_input, gamm
     return res_out, q
 
 
-def layernorm_q(x, gamma, beta, epsilon):
+def layernorm_q(x, gamma, beta, epsilon, fp32_norm=True):
     """int8 = clamp(rne(LayerNorm(x) * gamma + beta)) in one kernel.
-    Reference: LayerNormQ.forward, torch_int/nn/fused.py:13-18."""
+    Reference: LayerNormQ.forward, torch_int/nn/fused.py:13-18.  For fp16 x, fp32_norm=True normalises in
+    fp32 (the reference with fp32 parameters: it casts x to their dtype first); False rounds the LayerNorm
+    output to fp16 before quantising (the reference with parameters cast to fp16)."""
     _require(x, "x", None)
     kind = _float_kind(x, "x")
+    if kind == 1 and fp32_norm:
+        kind = 2
     h = x.shape[-1]
     rows = x.numel() // h if h else 0
     g, b = _affine(gamma, beta, h, x.device)

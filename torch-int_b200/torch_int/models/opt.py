@@ -451,6 +451,13 @@ class Int8OPTDecoder(nn.Module):
         self.layers = nn.ModuleList([
             Int8OPTDecoderLayer(config.hidden_size, config.num_attention_heads, config.ffn_dim, tp=self.tp)
             for _ in range(config.num_hidden_layers)])
+        # dtype of the residual stream between the layers.  torch.float32 (default): the embeddings are
+        # widened once and every residual update is exact fp32 arithmetic.  None: the dtype of the
+        # embeddings, as in the reference (opt.py:270-289 updates `hidden_states` in place), so a model
+        # held in fp16 - the reference benchmark's default precision "int8-fp16" - keeps an fp16 residual
+        # stream: each linear's fp32 output is cast to fp16 and added in fp16.  torch.float16 forces that.
+        # Tensor-parallel runs always use fp32 (the exchange kernels reduce into fp32 rows).
+        self.residual_dtype = torch.float32
 
     def get_input_embeddings(self):
         return self.embed_tokens
@@ -477,6 +484,13 @@ class Int8OPTDecoder(nn.Module):
         attn = self.layers[0].self_attn
         device = device if device is not None else self.embed_tokens.weight.device
         return StaticInt8KVCache(len(self.layers), batch_size, attn.local_heads, attn.head_dim, max_len, device)
+
+    def _stream_dtype(self, hidden):
+        """dtype of the residual stream for embeddings `hidden` (see residual_dtype)."""
+        want = self.residual_dtype if self.residual_dtype is not None else hidden.dtype
+        if self.tp.size > 1 or want not in (torch.float32, torch.float16):
+            return torch.float32
+        return want
 
     @staticmethod
     def _additive_mask(attention_mask, tgt_len, past_len, src_pad, dtype=torch.float32):
@@ -632,7 +646,7 @@ class Int8OPTDecoder(nn.Module):
             hidden = self.project_in(hidden)
         pos_ids = (cache.pos.long() + self.embed_positions.offset).view(1, 1).expand(bsz, 1)
         hidden = hidden + nn.functional.embedding(pos_ids, self.embed_positions.weight)
-        residual = hidden.to(torch.float32).contiguous()
+        residual = hidden.to(self._stream_dtype(hidden)).contiguous()
         first = self.layers[0].self_attn_layer_norm
         h8 = C.layernorm_q(residual, first.weight, first.bias, first.eps)
         n = len(self.layers)
@@ -686,7 +700,7 @@ class Int8OPTDecoder(nn.Module):
             for layer in self.layers:
                 residual = layer(residual, attention_mask=ref_mask)[0]
         else:
-            residual = hidden.to(torch.float32).contiguous()
+            residual = hidden.to(self._stream_dtype(hidden)).contiguous()
             chunks = self.tp.plan_chunks(bsz, tgt_len) if self.tp.size > 1 else 0
             if chunks:
                 residual = self._layers_pipelined(residual, cache, past_len, mask, chunks)

@@ -25,12 +25,14 @@ class LayerNormQ(_QuantisingNorm):
 
     def forward(self, x):
         # The reference casts x to the dtype of the affine parameters first (nn/fused.py:14), normally
-        # fp32.  The kernel's fp16 input path rounds the LayerNorm output to fp16 before quantising, which
-        # is what the reference computes only when the parameters themselves were cast to fp16; in every
-        # other case the input is widened (fp16 -> fp32 is exact) and the fp32 path runs.
-        keep_half = x.dtype == torch.float16 and self.weight.dtype != torch.float32
-        if x.dtype != torch.float32 and not keep_half:
+        # fp32, and normalises there; only when the parameters themselves were cast to fp16 is the
+        # LayerNorm output an fp16 tensor.  fp16 inputs are read as they are (no widening copy): the
+        # kernel converts on load.
+        half_params = self.weight.dtype == torch.float16
+        if x.dtype not in (torch.float32, torch.float16):
             x = x.to(torch.float32)
+        if x.dtype == torch.float16:
+            return layernorm_q(x.contiguous(), self.weight, self.bias, self.eps, fp32_norm=not half_params)
         return layernorm_q(x.contiguous(), self.weight, self.bias, self.eps)
 
     @staticmethod
