@@ -317,6 +317,10 @@ int ti_tp_barrier_limit(void* const* pads, int32_t rank, int32_t n, uint32_t epo
  * No reference counterpart (the reference has no multi-GPU path). */
 int ti_set_sm_limit(int sms);
 
+/* Tuning knob: number of M tiles per band of the GEMM tile order (0 = automatic: up to 32 CTA-pair tiles
+ * while the band's A rows stay below 32 MB, else 8).  No reference counterpart. */
+int ti_set_group_m(int tiles);
+
 /* ABI version of this header (bumped on incompatible changes). */
 int ti_abi_version(void);
 

@@ -144,6 +144,8 @@ def test_model_layer_shapes_full_tensor(cuda_ops, m, n, k, what):
     alpha = 1.0 / (60.0 * k ** 0.5)
     y = C.linear_relu_a8_w8_b8_o8(x.cuda(), w.cuda(), b8.cuda(), alpha, 0.05)
     assert_bit_exact(y, O.epilogue_s8_bias_s8(want, b8, alpha, 0.05, relu=True), what + " (ReLU int8)")
+    ws = C._split_k_workspace(torch.device("cuda", torch.cuda.current_device()))
+    assert int(ws.count_nonzero()) == 0, "the scratch of the split paths must be left zeroed"
     assert C.device_status() == 0
 
 

@@ -51,8 +51,11 @@ def build(force=False, verbose=False):
             sys.stderr.write(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    cmd = [_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-o", OUT] + objs + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+    # link next to the target and rename: a reader never sees a half-written library
+    tmp = OUT + ".tmp"
+    cmd = [_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-o", tmp] + objs + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
     subprocess.check_call(cmd)
+    os.replace(tmp, OUT)
     for o in objs:
         os.remove(o)
     return OUT

@@ -10,7 +10,10 @@
 //
 // Layouts (those of the static cache): keys [B, cap, Hl*D] rows; values transposed
 // [B, Hl, D, cap]; qkv [B, 3*Hl*D] = the fused projection output of the new token.
-// One CTA of 128 threads per (sequence, head); HBM-bound on the cache: (D + D) * (*pos + 1) bytes.
+// One CTA of 256 threads per (sequence, head); HBM-bound on the cache: (D + D) * (*pos + 1) bytes.
+// Key rows are read with one coalesced 128-byte row per 8 lanes and four rows in flight per lane, value
+// rows with 512-byte segments per warp and four rows in flight, so that the kernel is bound by
+// bandwidth rather than by a chain of dependent loads.
 #include <cuda_runtime.h>
 #include <float.h>
 #include <stdint.h>
@@ -45,16 +48,21 @@ __device__ __forceinline__ int warp_sum_i(int v) {
   return v;
 }
 
+constexpr int DEC_THREADS = 256;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(DEC_THREADS)
 decode_attention_s8_kernel(const int8_t* __restrict__ qkv, long long ld_qkv, int8_t* __restrict__ keys,
                            int8_t* __restrict__ values_t, int cap, int hl, const int* __restrict__ pos,
                            float alpha_qk, float alpha_pv, int8_t* __restrict__ ctx, long long ld_ctx,
                            int* status) {
+  constexpr int PIECES = D / 16;        // 16-byte pieces of a key row
+  constexpr int RPW = 32 / PIECES;      // key rows a warp covers with one load per lane
   extern __shared__ __align__(16) unsigned char dsm[];
   float* s_scores = reinterpret_cast<float*>(dsm);                 // [cap]
   int8_t* s_probs = reinterpret_cast<int8_t*>(dsm + cap * 4);      // [cap] (zero beyond the length)
-  __shared__ float red[8];
+  __shared__ float red[2 * DEC_WARPS];
   const int b = blockIdx.x / hl, h = blockIdx.x % hl;
   const int el = hl * D;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -69,62 +77,82 @@ decode_attention_s8_kernel(const int8_t* __restrict__ qkv, long long ld_qkv, int
   int8_t* vrows = values_t + (static_cast<long long>(b) * hl + h) * D * static_cast<long long>(cap);
 
   // append the new key row (D bytes) and value column (one byte in each of D rows)
-  if (tid < D / 16)
+  if (tid < PIECES)
     reinterpret_cast<uint4*>(krows + static_cast<long long>(len) * el)[tid] =
         reinterpret_cast<const uint4*>(qrow + el)[tid];
   if (tid < D) vrows[static_cast<long long>(tid) * cap + len] = qrow[2 * el + tid];
+  // this lane's 16 bytes of q
+  const int piece = lane % PIECES, sub = lane / PIECES;
+  const uint4 qp = reinterpret_cast<const uint4*>(qrow)[piece];
+  __syncthreads();  // the new key row and value column are visible to the whole CTA
 
-  // q in registers
-  uint4 q[D / 16];
-#pragma unroll
-  for (int i = 0; i < D / 16; ++i) q[i] = reinterpret_cast<const uint4*>(qrow)[i];
-  __syncthreads();  // the new key row is visible to the whole CTA
-
-  // scores: thread t takes rows t, t+128, ...
+  // ---- scores: PIECES lanes share a key row (one coalesced row per load), four rows in flight per lane
   float mx = -FLT_MAX;
-  for (int j = tid; j < S; j += 128) {
-    const uint4* kr = reinterpret_cast<const uint4*>(krows + static_cast<long long>(j) * el);
-    int acc = 0;
+  for (int base = warp * RPW * 4; base < S; base += DEC_WARPS * RPW * 4) {
+    uint4 kv[4];
 #pragma unroll
-    for (int i = 0; i < D / 16; ++i) acc = dot16(q[i], kr[i], acc);
-    const float s = alpha_qk * __int2float_rn(acc);
-    s_scores[j] = s;
-    mx = fmaxf(mx, s);
+    for (int u = 0; u < 4; ++u) {
+      const int j = base + u * RPW + sub;
+      kv[u] = j < S ? reinterpret_cast<const uint4*>(krows + static_cast<long long>(j) * el)[piece]
+                    : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int acc = dot16(qp, kv[u], 0);
+#pragma unroll
+      for (int o = 1; o < PIECES; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      const int j = base + u * RPW + sub;
+      if (piece == 0 && j < S) {
+        const float sc = alpha_qk * __int2float_rn(acc);
+        s_scores[j] = sc;
+        mx = fmaxf(mx, sc);
+      }
+    }
   }
   mx = warp_max_f(mx);
   if (lane == 0) red[warp] = mx;
   __syncthreads();
-  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  mx = red[0];
+#pragma unroll
+  for (int w = 1; w < DEC_WARPS; ++w) mx = fmaxf(mx, red[w]);
   float sum = 0.f;
-  for (int j = tid; j < S; j += 128) {
+  for (int j = tid; j < S; j += DEC_THREADS) {
     const float e = expf(s_scores[j] - mx);
     s_scores[j] = e;
     sum += e;
   }
   sum = warp_sum_f(sum);
-  __syncthreads();  // red[] reads above are done
-  if (lane == 0) red[4 + warp] = sum;
+  if (lane == 0) red[DEC_WARPS + warp] = sum;
   __syncthreads();
-  sum = (red[4] + red[5]) + (red[6] + red[7]);
+  sum = ((red[DEC_WARPS] + red[DEC_WARPS + 1]) + (red[DEC_WARPS + 2] + red[DEC_WARPS + 3])) +
+        ((red[DEC_WARPS + 4] + red[DEC_WARPS + 5]) + (red[DEC_WARPS + 6] + red[DEC_WARPS + 7]));
   const int s_pad = (S + 15) & ~15;
-  for (int j = tid; j < s_pad; j += 128) {
+  for (int j = tid; j < s_pad; j += DEC_THREADS) {
     int p = 0;
     if (j < S) p = max(-128, min(127, __float2int_rn(__fdiv_rn(s_scores[j], sum) * 127.f)));
     s_probs[j] = static_cast<int8_t>(p);
   }
   __syncthreads();
 
-  // context: warp w owns value rows d = w*(D/4) .. ; lanes stride over the positions 16 bytes at a time
-  for (int i = 0; i < D / 4; ++i) {
-    const int d = warp * (D / 4) + i;
-    const int8_t* vr = vrows + static_cast<long long>(d) * cap;
-    int acc = 0;
-    for (int j = lane * 16; j < s_pad; j += 512)
-      acc = dot16(*reinterpret_cast<const uint4*>(s_probs + j), *reinterpret_cast<const uint4*>(vr + j), acc);
-    acc = warp_sum_i(acc);
-    if (lane == 0) {
-      const int o = max(-128, min(127, __float2int_rn(alpha_pv * __int2float_rn(acc))));
-      ctx[b * ld_ctx + h * D + d] = static_cast<int8_t>(o);
+  // ---- context: a warp owns D/8 value rows and takes four at a time; lanes stride over the
+  //      positions 16 bytes at a time (one coalesced 512-byte segment of a row per load)
+  constexpr int ROWS = D / DEC_WARPS;
+#pragma unroll 1
+  for (int dd = 0; dd < ROWS; dd += 4) {
+    const int d0 = warp * ROWS + dd;
+    int acc[4] = {0, 0, 0, 0};
+    for (int j = lane * 16; j < s_pad; j += 512) {
+      const uint4 pp = *reinterpret_cast<const uint4*>(s_probs + j);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        acc[u] = dot16(pp, *reinterpret_cast<const uint4*>(vrows + static_cast<long long>(d0 + u) * cap + j), acc[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = warp_sum_i(acc[u]);
+    if (lane < 4) {
+      const int a = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+      const int o = max(-128, min(127, __float2int_rn(alpha_pv * __int2float_rn(a))));
+      ctx[b * ld_ctx + h * D + d0 + lane] = static_cast<int8_t>(o);
     }
   }
 }
@@ -168,14 +196,14 @@ int decode_attention_s8(const int8_t* qkv, int64_t ld_qkv, int8_t* keys, int8_t*
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(decode_attention_s8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem));
-    decode_attention_s8_kernel<128><<<grid, 128, smem, stream>>>(
+    decode_attention_s8_kernel<128><<<grid, DEC_THREADS, smem, stream>>>(
         qkv, ld_qkv, keys, values_t, static_cast<int>(cap), static_cast<int>(local_heads), pos, alpha_qk,
         alpha_pv, ctx, ld_ctx, status);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(decode_attention_s8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem));
-    decode_attention_s8_kernel<64><<<grid, 128, smem, stream>>>(
+    decode_attention_s8_kernel<64><<<grid, DEC_THREADS, smem, stream>>>(
         qkv, ld_qkv, keys, values_t, static_cast<int>(cap), static_cast<int>(local_heads), pos, alpha_qk,
         alpha_pv, ctx, ld_ctx, status);
   }

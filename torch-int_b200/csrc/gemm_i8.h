@@ -66,6 +66,9 @@ int split_k_auto_splits(int64_t M, int64_t N, int64_t K);
 // Caps the number of SMs the persistent GEMM grids use (0 = all SMs of the device).
 void set_sm_limit(int sms);
 
+// Tuning knob: M tiles per rasterisation band of the GEMM tile order (0 = automatic).
+void set_group_m(int tiles);
+
 // Tensor map (CUtensorMap, 128 bytes, passed as an opaque pointer so that this header needs no
 // driver API types) of a K-major int8 operand [batch2, batch, rows, K]: box = 128 bytes of K x
 // box_rows x 1 x 1, 128-byte swizzle, out-of-range elements read as zero.  A batch index of extent

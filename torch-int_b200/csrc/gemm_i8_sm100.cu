@@ -125,6 +125,12 @@ __device__ __forceinline__ TileCoord decode_tile(long long t, const KernelParams
   return c;
 }
 
+// Fire-and-forget integer add to global memory: `red` returns nothing, so a thread keeps issuing
+// the next ones while these are on their way to L2.
+__device__ __forceinline__ void red_add_s32(int32_t* addr, int v) {
+  asm volatile("red.relaxed.gpu.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ int sat_rne_s8(float y) {
   int v = __float2int_rn(y);  // cvt.rni.s32.f32: RNE, saturating, NaN -> 0
   return max(-128, min(127, v));
@@ -396,9 +402,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int col = n0 + c * 32 + lane;
             if (col < p.N) {
               int32_t* wcol = p.ws + static_cast<long long>(row0) * p.N + col;
+#pragma unroll 4
               for (int r = 0; r < valid; ++r)
-                atomicAdd(wcol + static_cast<long long>(r) * p.N,
-                          *reinterpret_cast<const int*>(patch + r * 144 + lane * 4));
+                red_add_s32(wcol + static_cast<long long>(r) * p.N,
+                            *reinterpret_cast<const int*>(patch + r * 144 + lane * 4));
             }
           }
         }
@@ -631,6 +638,8 @@ namespace {
 // Upper bound on the SMs the persistent GEMM grid occupies (0 = all).  A caller that
 // overlaps collectives with the GEMMs lowers it so that the collective's CTAs find free SMs.
 int g_sm_limit = 0;
+// Rasterisation band override for tuning (0 = choose automatically).
+int g_group_m = 0;
 
 int num_sms() {
   static int cached[64] = {0};
@@ -693,7 +702,17 @@ int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
   p.beta = g.beta;
   p.alpha_vec = g.alpha_vec;
   p.beta_vec = g.beta_vec;
+  // Rasterisation band: M tiles swept per pass over the N tiles.  Wide bands re-read B less often but
+  // need the band's A rows to stay in L2.  Measured on the model shapes (M = 4096): a band of 16 pair
+  // tiles wins while its A rows stay below about 32 MB (K <= 8192: out_proj 165 -> 147 us, q/k/v
+  // 479 -> 440 us), bands of 8 win beyond (K = 12288, 28672).
   p.group_m = PAIR ? 8 : 16;
+  if (g_group_m > 0) {
+    p.group_m = g_group_m;
+  } else if (PAIR) {
+    const int gm = p.m_tiles < 32 ? p.m_tiles : 32;
+    if (gm > 8 && static_cast<long long>(gm) * C::TILE_M * g.K <= (32ll << 20)) p.group_m = gm;
+  }
   p.a_b1 = (g.strideA != 0 && g.batch > 1) ? 1 : 0;
   p.a_b2 = (g.stride2A != 0 && g.batch2 > 1) ? 1 : 0;
   p.b_b1 = (g.strideB != 0 && g.batch > 1) ? 1 : 0;
@@ -1016,6 +1035,8 @@ int* status_word_ptr() {
 int64_t split_k_workspace_bytes(int64_t M, int64_t N) { return counter_bytes(32, N) + M * N * 4; }
 
 void set_sm_limit(int sms) { g_sm_limit = sms > 0 ? sms : 0; }
+
+void set_group_m(int tiles) { g_group_m = tiles > 0 ? tiles : 0; }
 
 // Reads (and optionally clears) the status word the kernels of this file set
 // when a bounded wait gives up.  Synchronises the device.

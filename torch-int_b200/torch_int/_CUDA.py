@@ -112,6 +112,7 @@ _c_last_error = _sig("ti_last_error", [], ctypes.c_char_p)
 _c_device_status = _sig("ti_device_status", [ctypes.POINTER(ctypes.c_int), _i32])
 _c_abi_version = _sig("ti_abi_version", [])
 _c_set_sm_limit = _sig("ti_set_sm_limit", [_i32])
+_c_set_group_m = _sig("ti_set_group_m", [_i32])
 
 if _c_abi_version() != 1:
     raise ImportError("torch_int._CUDA: libtorch_int_b200.so has an unexpected ABI version")
@@ -606,6 +607,11 @@ def transpose_values(v, vt, col0=0):
                                  _stream_ptr(v.device))
     _check(rc)
     return vt
+
+
+def set_group_m(tiles):
+    """Tuning knob: M tiles per band of the GEMM tile order (0 = automatic); see ti_set_group_m."""
+    _c_set_group_m(int(tiles))
 
 
 def set_sm_limit(sms):

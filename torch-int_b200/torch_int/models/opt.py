@@ -641,6 +641,11 @@ class Int8OPTDecoder(nn.Module):
         sequence of launches with fixed arguments: it can be captured once in a CUDA graph and
         replayed.  Returns the last hidden state [B,1,proj]."""
         bsz = tokens.shape[0]
+        if self.layers[0].self_attn.head_dim not in (64, 128):
+            # the one-token attention kernel covers head_dim 64 and 128 (all OPT sizes but 2.7B, whose
+            # heads are 80 wide); other widths take the prefill path with one query row per sequence,
+            # which reads the position on the host and therefore cannot be replayed from a CUDA graph
+            return self.forward(tokens, past_key_values=cache, use_cache=True).last_hidden_state
         hidden = self.embed_tokens(tokens)
         if self.project_in is not None:
             hidden = self.project_in(hidden)
@@ -854,8 +859,11 @@ class Int8OPTForCausalLM(nn.Module):
             cache.reset()
         if t + max_new_tokens > cache.capacity:
             raise RuntimeError(f"cache capacity {cache.capacity} is too small for {t} + {max_new_tokens} tokens")
+        dec = self.model.decoder
+        graph_ok = dec.tp.size == 1 and dec.layers[0].self_attn.head_dim in (64, 128)
         if use_cuda_graph is None:
-            use_cuda_graph = self.model.decoder.tp.size == 1
+            use_cuda_graph = graph_ok
+        use_cuda_graph = use_cuda_graph and graph_ok
         out = self.forward(input_ids, past_key_values=cache, use_cache=True, last_token_only=True)
         tokens = [input_ids]
         nxt = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
