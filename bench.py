@@ -161,7 +161,8 @@ def dist_env():
 # DRAM traffic per launch of gemm_i8_kernel, from ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # captured launch; the summaries under profiles/ give the commands).  Keyed by (M, N, K).
 NCU_GEMM_TRAFFIC_BYTES = {
-    (4096, 12288, 12288): 474.7e6,
+    (4096, 12288, 12288): 462.1e6,   # profiles/gemm_i8_pair_4096x12288x12288.md
+    (4096, 28672, 7168): 344.0e6,    # profiles/gemm_i8_pair_fc1_4096x28672x7168.md
 }
 
 
@@ -414,7 +415,7 @@ class OptWorkload:
         for _ in range(3):
             nxt = model.decode_step(nxt, cache).argmax(dim=-1, keepdim=True)
         graph = None
-        if self.world == 1:
+        if self.world == 1 or self.tp.decode_graph:
             static_tok = nxt.clone()
             length = cache.length
             graph = torch.cuda.CUDAGraph()
@@ -780,6 +781,9 @@ def run_reference(args, world, rank):
         run()
     dt = time.perf_counter() - t0
     value = units * steps / dt
+    extra = {}
+    if key == "gemm":
+        extra = reference_cuda_kernel_rate()
     line = {"impl": "reference", "metric": metric, "value": round(value, 4), "unit": unit,
             "n_gpus": world, "steps": steps, "warmup": args.warmup,
             "ms_per_step": round(dt / steps * 1e3, 3), "higher_is_better": True, "scaling": scaling,
@@ -788,7 +792,33 @@ def run_reference(args, world, rank):
             "cpu_baseline": {"value": round(value, 4), "unit": unit, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": round(value, 4), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    line.update(extra)
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_kernel_rate():
+    """Extra key of the CPU arm's gemm line, when a GPU and the reference's own extension are there
+    (oracle/_ref/ref_torch_int.so: its CUTLASS 2.x Sm80 mma.sync kernels, built from the reference's sources and
+    translated by the driver for this GPU): TOP/s of the reference's linear_a8_w8_b8_o8 on the headline shape.
+    Informational - the arm's `value` stays the host-core figure."""
+    try:
+        if not torch.cuda.is_available():
+            return {}
+        from oracle import build_ref_gemm
+        ref = build_ref_gemm.load()
+        if ref is None:
+            return {}
+        m, n, k = HG
+        dev = torch.device("cuda", 0)
+        x = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 128, (n,), dtype=torch.int8, device=dev)
+        ms = _event_time(lambda: ref.linear_a8_w8_b8_o8(x, w, b, 1e-4, 0.01), 20)
+        return {"reference_cuda_kernel": {"op": "linear_a8_w8_b8_o8 (CUTLASS 2.x Sm80 mma.sync, PTX translated for this GPU)",
+                                          "shape": [m, n, k], "ms": round(ms, 4),
+                                          "tops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1)}}
+    except Exception as exc:  # noqa: BLE001 - an optional extra must not break the arm
+        return {"reference_cuda_kernel": {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}}
 
 
 def profile_one_step(wl, region):
@@ -831,6 +861,9 @@ def main():
                          "trace format) and add the per-stream busy times to the JSON line")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for ncu: no end-to-end leg, no CPU baseline")
+    ap.add_argument("--shape", default=None, metavar="M,N,K",
+                    help="gemm workload: another problem size than the headline one (for profiler captures of the "
+                         "models' per-layer GEMMs; the line then names that shape)")
     ap.add_argument("--profile-region", default=None, choices=["prefill", "decode"],
                     help="OPT workloads, one GPU: after warm-up, run ONE prefill step or ONE eager decode step between "
                          "cudaProfilerStart/Stop and exit (for `ncu --profile-from-start off`: the launch list of a step)")
@@ -861,6 +894,10 @@ def main():
                                 timeout=datetime.timedelta(seconds=int(os.environ.get("TI_BENCH_NCCL_TIMEOUT_S", "120"))))
         progress("process group initialised")
     if key == "gemm":
+        if args.shape:
+            global HG
+            HG = tuple(int(v) for v in args.shape.split(","))
+            GemmWorkload.name = "w8a8_gemm_%dx%dx%d_int8out" % HG
         wl = GemmWorkload(device)
     elif key == "norm":
         wl = RowKernelWorkload(device)

@@ -53,6 +53,13 @@ def _rank_main(rank, world, port, ret, big):
         logits4 = tp_model(ids4).logits                     # several groups: pipelined exchanges
         again = tp_model(ids4).logits                       # a second pass over the same workspace
         gen = tp_model.generate_greedy(ids4[:, :prompt], new)   # static cache, one-token steps
+        if not big:
+            # the default replays the steps from a CUDA graph that contains the NCCL all-reduces: same tokens
+            # as eager steps
+            assert tp_model.model.decoder.tp.decode_graph
+            eager = tp_model.generate_greedy(ids4[:, :prompt], new, use_cuda_graph=False)
+            if not torch.equal(gen, eager):
+                raise AssertionError("graph replay of tensor-parallel decode steps differs from eager steps")
         tp = tp_model.model.decoder.tp
         extra_ok = True
         if not big:

@@ -860,7 +860,9 @@ class Int8OPTForCausalLM(nn.Module):
         if t + max_new_tokens > cache.capacity:
             raise RuntimeError(f"cache capacity {cache.capacity} is too small for {t} + {max_new_tokens} tokens")
         dec = self.model.decoder
-        graph_ok = dec.tp.size == 1 and dec.layers[0].self_attn.head_dim in (64, 128)
+        # tensor-parallel steps contain NCCL all-reduces; capturing them needs every rank to capture and
+        # replay in lockstep, which generate_greedy does (opt-in: TensorParallel.decode_graph)
+        graph_ok = (dec.tp.size == 1 or dec.tp.decode_graph) and dec.layers[0].self_attn.head_dim in (64, 128)
         if use_cuda_graph is None:
             use_cuda_graph = graph_ok
         use_cuda_graph = use_cuda_graph and graph_ok

@@ -101,12 +101,19 @@ class TensorParallel:
         # SMs the GEMM grids may use while exchanges overlap them (0 = all); TI_TP_GEMM_SMS overrides
         self.gemm_sm_limit = int(os.environ.get("TI_TP_GEMM_SMS", "0"))
         # 1: one communication stream carries copy -> barrier -> reduce+LayerNorm -> barrier of each
-        # exchange back to back.  2: the copies (+ first barrier) and the reduce kernel (+ second barrier)
-        # run on two streams, so the copies of the next group overlap the reduction of this one.
-        self.comm_streams = int(os.environ.get("TI_TP_COMM_STREAMS", "1"))
-        # True: the two barriers of an exchange are folded into the reduce kernel (one launch per
-        # exchange after the copies); False: barrier kernel -> reduce kernel -> barrier kernel
-        self.fused_sync = os.environ.get("TI_TP_FUSED_SYNC", "1") != "0"
+        # exchange back to back.  2 (default): the copies (+ first barrier) and the reduce kernel (+ second
+        # barrier) run on two streams, so the copies of the next group overlap the reduction of this one
+        # (8 ranks, OPT-175B: one stream is busy 440 ms of a 455 ms step; two streams give 445 ms).
+        self.comm_streams = int(os.environ.get("TI_TP_COMM_STREAMS", "2"))
+        # False (default): barrier kernel -> reduce kernel -> barrier kernel.  True: the two barriers of
+        # an exchange are folded into the reduce kernel (one launch per exchange after the copies).
+        # Measured at 8 ranks (OPT-175B, batch 16 x 1024): 455 ms per step with the separate barrier
+        # kernels, 470 ms folded - while a folded kernel waits for a slower rank, its 512 CTAs hold
+        # the registers the next GEMM needs, whereas a waiting barrier kernel is one warp.
+        self.fused_sync = os.environ.get("TI_TP_FUSED_SYNC", "0") == "1"
+        # replay tensor-parallel decode steps (which contain NCCL all-reduces) from a CUDA graph: eager
+        # steps are bound by the host's launch rate (31 ms per step at 4 and 8 ranks of OPT-175B)
+        self.decode_graph = os.environ.get("TI_TP_DECODE_GRAPH", "1") != "0"
         # a StreamTrace while a forward pass is being traced, else None
         self.trace: Optional[StreamTrace] = None
         # language-model head split by vocabulary rows: each rank multiplies with its 1/size of the
