@@ -321,6 +321,13 @@ int ti_set_sm_limit(int sms);
  * while the band's A rows stay below 32 MB, else 8).  No reference counterpart. */
 int ti_set_group_m(int tiles);
 
+/* Small-M GEMMs (M <= 128: decode steps) are launched with programmatic stream serialisation by default:
+ * their CTAs may become resident while the kernel before them in the stream drains and fetch their first
+ * weight tiles (model constants that no kernel writes); activations, outputs and scratch are touched only after
+ * the earlier kernel has completed.  A caller that overwrites WEIGHTS with a kernel on the same stream right
+ * before such a GEMM turns this off (on = 0).  No reference counterpart. */
+int ti_set_dependent_launch(int on);
+
 /* ABI version of this header (bumped on incompatible changes). */
 int ti_abi_version(void);
 

@@ -152,3 +152,34 @@ def test_from_float_matches_the_reference_modules(golden_dir):
     q = LayerNormQ.from_float(ln, float(z["ln_output_scale"]))
     assert np.array_equal(q.weight.numpy(), z["lnq_weight"]) and np.array_equal(q.bias.numpy(), z["lnq_bias"])
     assert q.eps == float(z["ln_eps"])
+
+
+@pytest.mark.gpu
+def test_status_reset_clears_the_split_k_workspace(monkeypatch):
+    """A launch that gave up on a bounded wait may leave partial sums in the split-K scratch, which every later
+    small-M GEMM expects all zero: device_status(reset=True) must hand it back zeroed together with the status
+    word.  The non-zero status is injected on the host (no kernel is made to time out)."""
+    from torch_int import _CUDA as C
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ws = C._split_k_workspace(dev)
+    ws[:4096].fill_(7)
+    real = C._c_device_status
+
+    def fake(status_ptr, reset):
+        real(status_ptr, reset)
+        status_ptr._obj.value = 105          # byref(c_int) -> the c_int the caller reads afterwards
+        return 0
+    monkeypatch.setattr(C, "_c_device_status", fake)
+    assert C.device_status(reset=False) == 105 and int(ws.count_nonzero()) == 4096   # reading alone changes nothing
+    assert C.device_status(reset=True) == 105
+    assert int(ws.count_nonzero()) == 0
+    monkeypatch.undo()
+    assert C.device_status() == 0
+    # and a small-M linear through the cleared scratch is right
+    from oracle import w8a8 as O
+    g = torch.Generator().manual_seed(1)
+    x = torch.randint(-127, 128, (8, 4096), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (2048, 4096), generator=g, dtype=torch.int8)
+    b = torch.randint(-127, 128, (2048,), generator=g, dtype=torch.int8)
+    assert torch.equal(C.linear_a8_w8_b8_o8(x.cuda(), w.cuda(), b.cuda(), 2e-4, 0.01).cpu(),
+                       O.linear_a8_w8_b8_o8(x, w, b, 2e-4, 0.01))

@@ -309,6 +309,11 @@ int ti_set_sm_limit(int sms) {
   return TI_OK;
 }
 
+int ti_set_dependent_launch(int on) {
+  set_dependent_launch(on);
+  return TI_OK;
+}
+
 int ti_set_group_m(int tiles) {
   set_group_m(tiles);
   return TI_OK;

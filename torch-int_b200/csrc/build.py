@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(os.path.dirname(HERE), "torch_int", "lib")
 OUT = os.path.join(OUT_DIR, "libtorch_int_b200.so")
 SOURCES = ["gemm_i8_sm100.cu", "norm_quant.cu", "decode_attention.cu", "attention_prefill_sm100.cu", "abi.cu"]
-HEADERS = ["gemm_i8.h", "norm_quant.h", "attention_prefill.h", "sm100_ptx.cuh",
+HEADERS = ["gemm_i8.h", "norm_quant.h", "attention_prefill.h", "sm100_ptx.cuh", "grid_dependency.cuh",
            os.path.join("..", "..", "include", "torch_int_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -19,6 +19,7 @@
 #include <stdint.h>
 
 #include "gemm_i8.h"
+#include "grid_dependency.cuh"
 #include "norm_quant.h"
 
 namespace ti {
@@ -66,6 +67,8 @@ decode_attention_s8_kernel(const int8_t* __restrict__ qkv, long long ld_qkv, int
   const int b = blockIdx.x / hl, h = blockIdx.x % hl;
   const int el = hl * D;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_dep_launch();  // the out_proj GEMM that follows may start fetching its weights now ...
+  grid_dep_wait();    // ... and this kernel reads the q/k/v rows the GEMM before it wrote
   const int len = *pos;  // keys/values already cached; the new token goes to position `len`
   if (len < 0 || len >= cap) {
     if (tid == 0) atomicCAS(status, 0, 201);  // cache full: refuse instead of writing out of bounds

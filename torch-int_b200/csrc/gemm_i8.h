@@ -69,6 +69,10 @@ void set_sm_limit(int sms);
 // Tuning knob: M tiles per rasterisation band of the GEMM tile order (0 = automatic).
 void set_group_m(int tiles);
 
+// Small-M GEMMs (decode steps) are launched with programmatic stream serialisation (default on): they
+// start fetching weights while the kernel before them drains.  0 turns that off.
+void set_dependent_launch(int on);
+
 // Tensor map (CUtensorMap, 128 bytes, passed as an opaque pointer so that this header needs no
 // driver API types) of a K-major int8 operand [batch2, batch, rows, K]: box = 128 bytes of K x
 // box_rows x 1 x 1, 128-byte swizzle, out-of-range elements read as zero.  A batch index of extent

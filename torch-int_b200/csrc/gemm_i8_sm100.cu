@@ -65,6 +65,11 @@ struct KernelParams {
   int splits, kb_per_split;
   int32_t* ws;
   int* counters;
+  // 1: launched with programmatic stream serialisation (small-M problems): the kernel may start while
+  // the kernel before it still runs.  The B operand is model weights, which no kernel writes, so the
+  // producer fetches the B tiles of its first stages at once; everything else (A, the outputs, the
+  // split-K scratch) is touched only after grid_dep_wait().
+  int pdl;
 };
 
 // PAIR = false: one CTA computes a 128 x BN tile (tcgen05 cta_group::1).
@@ -234,6 +239,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) grid_dep_launch();  // the next kernel may be scheduled as CTAs of this one drain
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -241,11 +247,36 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int prefetched = 0;  // K blocks of the first work item whose stages were filled before the loop
+      if constexpr (!PAIR) {
+        if (p.pdl && first_tile < p.total_tiles) {
+          // weights first: they do not depend on the kernel before this one
+          const TileCoord tc = decode_tile(first_tile, p);
+          const int row_a = tc.m_tile * C::TILE_M;
+          const int row_b = tc.n_tile * BN;
+          const int n = min(C::STAGES, tc.kb1 - tc.kb0);
+          for (int s = 0; s < n; ++s) {
+            const uint32_t fb = smem_u32(&full_bar[s]);
+            mbar_expect_tx(fb, C::STAGE_BYTES);
+            tma_load_4d(smem_u32(smem + s * C::STAGE_BYTES + C::A_BYTES), &tmap_b, fb, (tc.kb0 + s) * BK, row_b,
+                        tc.b1 * p.b_b1, tc.b2 * p.b_b2);
+          }
+          grid_dep_wait();  // the activations are the output of the kernel before
+          for (int s = 0; s < n; ++s)
+            tma_load_4d(smem_u32(smem + s * C::STAGE_BYTES), &tmap_a, smem_u32(&full_bar[s]), (tc.kb0 + s) * BK, row_a,
+                        tc.b1 * p.a_b1, tc.b2 * p.a_b2);
+          prefetched = n;
+          stage = n == C::STAGES ? 0 : n;
+          phase = n == C::STAGES ? 1 : 0;
+        }
+      }
       for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step) {
         const TileCoord tc = decode_tile(t, p);
         const int row_a = tc.m_tile * C::TILE_M + static_cast<int>(rank) * BM;
         const int row_b = tc.n_tile * BN + static_cast<int>(rank) * C::B_ROWS;
-        for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
+        const int kb_first = tc.kb0 + prefetched;
+        prefetched = 0;
+        for (int kb = kb_first; kb < tc.kb1; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, TI_ERR_WAIT_EMPTY);
           if (!ok) break;
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
@@ -330,6 +361,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    if (p.pdl) grid_dep_wait();  // outputs and the split-K scratch may still be in use by the kernel before
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     const int et = threadIdx.x - 64;
     int it = 0;
@@ -640,6 +672,8 @@ namespace {
 int g_sm_limit = 0;
 // Rasterisation band override for tuning (0 = choose automatically).
 int g_group_m = 0;
+// Small-M launches use programmatic dependent launch (1) or ordinary stream order (0).
+int g_pdl = 1;
 
 int num_sms() {
   static int cached[64] = {0};
@@ -723,6 +757,7 @@ int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
   p.kb_per_split = p.num_kb;
   p.ws = nullptr;
   p.counters = nullptr;
+  p.pdl = (!PAIR && g_pdl && g.M <= BM && g.scatter_rows == 0) ? 1 : 0;
   if (!PAIR && splits > 1) {
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
@@ -742,13 +777,15 @@ int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = PAIR ? 2 : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = p.pdl ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_kernel<BN, EPI, PAIR>, ta, tb, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -1037,6 +1074,8 @@ int64_t split_k_workspace_bytes(int64_t M, int64_t N) { return counter_bytes(32,
 void set_sm_limit(int sms) { g_sm_limit = sms > 0 ? sms : 0; }
 
 void set_group_m(int tiles) { g_group_m = tiles > 0 ? tiles : 0; }
+
+void set_dependent_launch(int on) { g_pdl = on ? 1 : 0; }
 
 // Reads (and optionally clears) the status word the kernels of this file set
 // when a bounded wait gives up.  Synchronises the device.

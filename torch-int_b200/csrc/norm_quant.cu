@@ -14,6 +14,7 @@
 #include <stdint.h>
 
 #include "gemm_i8.h"
+#include "grid_dependency.cuh"
 #include "norm_quant.h"
 
 namespace ti {
@@ -147,6 +148,8 @@ layernorm_q_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                    const float* __restrict__ beta, float eps, int8_t* __restrict__ q, int H,
                    long long ldx, long long ldq) {
   __shared__ float scratch[32];
+  grid_dep_launch();  // a small-M GEMM that follows may start fetching its weights now ...
+  grid_dep_wait();    // ... and this kernel reads the output of the one before it
   const long long row = blockIdx.x;
   const int h4 = H >> 2;
   const T* xr = x + row * ldx;
@@ -166,6 +169,8 @@ dq_add_layernorm_q_kernel(const int32_t* __restrict__ in, float scale, const T* 
                           const float* __restrict__ beta, float eps, T* __restrict__ res_out,
                           int8_t* __restrict__ q, int H) {
   __shared__ float scratch[32];
+  grid_dep_launch();  // a small-M GEMM that follows may start fetching its weights now ...
+  grid_dep_wait();    // ... and this kernel reads the output of the one before it
   const long long row = blockIdx.x;
   const int h4 = H >> 2;
   const int32_t* ir = in + row * H;

@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "grid_dependency.cuh"
+
 #ifndef TI_WAIT_LIMIT_NS
 #define TI_WAIT_LIMIT_NS 2000000000ull  // 2 s per wait
 #endif
