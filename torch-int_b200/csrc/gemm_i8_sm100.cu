@@ -848,40 +848,52 @@ void choose_tile(const GemmProblem& g, int* bn_out, bool* pair_out) {
   *pair_out = best_pair;
 }
 
-// Number of K splits for a small-M problem with N tile `bn_split` (1 = none).  `wanted` > 1 asks for
-// that many (capped so that a split keeps at least 8 K blocks); 0 chooses: the cost, in K blocks, is
-// (rounds of the persistent grid) x (K blocks per work item + a charge for the workspace reduction and
-// the last-CTA epilogue).
-int choose_splits(int64_t N, int64_t K, int bn_split, int wanted) {
+// Tile width and number of K splits for a small-M problem (weights streamed once, HBM bound).  Model, in
+// microseconds, fitted to measurements at M = 8 on the OPT-30B decode shapes: a work item costs
+// (K blocks per item) x (bytes of B per K block = 128 x bn) / (an SM's share of HBM bandwidth, 44 B/ns)
+// plus 4.3 us for the pipeline fill, the partial-sum reduction and the last-CTA epilogue; the launch
+// takes as many such rounds as the busiest CTA of the persistent grid has items.  `force_bn` != 0
+// restricts the tile width, `wanted` > 1 asks for that many splits (capped so that a split keeps at
+// least 8 K blocks).
+void choose_small_m(int64_t N, int64_t K, int force_bn, int wanted, int* bn_out, int* splits_out) {
   const long long num_kb = (K + BK - 1) / BK;
-  const long long tiles = (N + bn_split - 1) / bn_split;
   const long long sms = num_sms();
   long long max_splits = num_kb / 8 > 0 ? num_kb / 8 : 1;
   if (max_splits > 64) max_splits = 64;
-  int splits = 1;
-  if (wanted > 1) {
-    splits = static_cast<int>(wanted < max_splits ? wanted : max_splits);
-  } else if (tiles < sms) {
-    long long best_cost = num_kb * ((tiles + sms - 1) / sms);
-    for (long long sp = 2; sp <= max_splits; ++sp) {
+  const int cands[3] = {256, 128, 64};
+  double best = 1e300;
+  int best_bn = force_bn ? force_bn : 128, best_sp = 1;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cands[i];
+    if (force_bn && bn != force_bn) continue;
+    if (!force_bn && bn > 64 && bn / 2 >= N) continue;  // tile mostly padding
+    const long long tiles = (N + bn - 1) / bn;
+    const long long lo = wanted > 1 ? (wanted < max_splits ? wanted : max_splits) : 1;
+    const long long hi = wanted > 1 ? lo : (wanted == 1 ? 1 : max_splits);
+    for (long long sp = lo; sp <= hi; ++sp) {
       const long long per = (num_kb + sp - 1) / sp;
-      const long long eff = (num_kb + per - 1) / per;
+      const long long eff = (num_kb + per - 1) / per;  // no empty split
       const long long rounds = (tiles * eff + sms - 1) / sms;
-      const long long cost = rounds * (per + 6);
-      if (cost < best_cost) {
-        best_cost = cost;
-        splits = static_cast<int>(eff);
+      const double cost = static_cast<double>(rounds) * (static_cast<double>(per) * bn * 0.0029 + 4.3) +
+                          (eff > 1 ? 0.0 : -1.0);  // no scratch traffic at all without a split
+      if (cost < best * 0.999) {
+        best = cost;
+        best_bn = bn;
+        best_sp = static_cast<int>(eff);
       }
     }
   }
-  return splits;
+  *bn_out = best_bn;
+  *splits_out = best_sp;
 }
 
 }  // namespace
 
 int split_k_auto_splits(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || M > BM || N <= 0 || K <= 0) return 1;
-  return choose_splits(N, K, N >= 4096 ? 128 : 64, 0);
+  int bn = 0, splits = 1;
+  choose_small_m(N, K, 0, 0, &bn, &splits);
+  return splits;
 }
 
 int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
@@ -977,9 +989,9 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
       set_error("split-K workspace must be 256-byte aligned");
       return TI_E_INVALID;
     }
-    const int bn_split = g.force_bn ? bn : (g.N >= 4096 ? 128 : 64);
-    splits = choose_splits(g.N, g.K, bn_split, g.splits);
-    if (splits > 1) bn = bn_split;  // otherwise keep the tile the general chooser picked
+    int bn_small = bn;
+    choose_small_m(g.N, g.K, g.force_bn, g.splits, &bn_small, &splits);
+    bn = bn_small;  // with or without a split: the width that streams the weights fastest
   }
   switch (g.epilogue) {
     case EPI_S8_BIAS_S8: return launch_bn<EPI_S8_BIAS_S8>(g, bn, pair, splits, stream);
