@@ -19,7 +19,8 @@
 // keys [0, 64) of every tile, the other keys [64, 128); each keeps a running maximum and sum of its
 // keys, the two are combined once after pass 1.  A thread copies its 64 accumulators into registers
 // and releases S immediately, so the next Q.K^T runs while the exponentials of this tile are evaluated.
-// Key tiles entirely below the diagonal take a mask-free path.  TMEM: 128 columns S + up to 128
+// The accumulators become fp32 scores in place, with the causal mask folded in as -FLT_MAX on the diagonal
+// tile only; all later loops are the same code for every tile (small enough for the instruction cache).  TMEM: 128 columns S + up to 128
 // columns O = 256 of 512, shared memory 99 KB: two CTAs per SM.  Only keys j <= t + past are visited
 // (causal); an explicit additive mask is not supported - callers with padding masks use the
 // three-kernel path.  Every wait is bounded (2 s) and reports through the status word.
@@ -260,7 +261,6 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_s + lane_off + half * 64;
     const float alpha = p.alpha_qk;
-    const bool alpha_neg = alpha < 0.f;
     constexpr float kLog2e = 1.4426950408889634f;
     // the fp32 score exactly as the unfused path stores it: one rounded multiply (never contracted
     // into the following subtraction)
@@ -280,6 +280,24 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       mbar_arrive(smem_u32(s_empty));
       ++g;
     };
+    // Accumulators -> fp32 scores in place (the registers keep the float bits), with the causal mask
+    // folded in as -FLT_MAX: everything after this step is the same code for tiles below and on the
+    // diagonal, which keeps the unrolled loops small enough for the instruction cache.
+    auto to_scores = [&](int c0, bool all_visible) {
+      if (all_visible) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          va[i] = __float_as_uint(score(va[i]));
+          vb[i] = __float_as_uint(score(vb[i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          va[i] = __float_as_uint(c0 + i <= lim ? score(va[i]) : -FLT_MAX);
+          vb[i] = __float_as_uint(c0 + 32 + i <= lim ? score(vb[i]) : -FLT_MAX);
+        }
+      }
+    };
     // ---- pass 1: row maximum and row sum over this thread's keys
 #pragma unroll 1
     for (int j = 0; j < nt && ok; ++j) {
@@ -287,48 +305,23 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       if (!ok) break;
       const int c0 = j * TILE_ROWS + half * 64;
       const bool all_visible = c0 + 63 <= t0 + p.past;  // for every valid row of the CTA (uniform)
-      // the largest score = the score of the largest (alpha < 0: smallest) accumulator
-      int best = alpha_neg ? INT_MAX : INT_MIN;
-      bool any = all_visible;
-      if (all_visible) {
+      if (!all_visible && c0 > lim) continue;  // none of this thread's keys of this tile is visible to its row
+      to_scores(c0, all_visible);
+      float t0m = -FLT_MAX, t1m = -FLT_MAX;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int a0 = static_cast<int>(va[i]), a1 = static_cast<int>(vb[i]);
-          best = alpha_neg ? min(best, min(a0, a1)) : max(best, max(a0, a1));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (c0 + i <= lim) {
-            best = alpha_neg ? min(best, static_cast<int>(va[i])) : max(best, static_cast<int>(va[i]));
-            any = true;
-          }
-          if (c0 + 32 + i <= lim) {
-            best = alpha_neg ? min(best, static_cast<int>(vb[i])) : max(best, static_cast<int>(vb[i]));
-            any = true;
-          }
-        }
+      for (int i = 0; i < 32; ++i) {
+        t0m = fmaxf(t0m, __uint_as_float(va[i]));
+        t1m = fmaxf(t1m, __uint_as_float(vb[i]));
       }
-      if (!any) continue;  // none of this thread's keys of this tile is visible to its row
-      const float mn = fmaxf(m, score(static_cast<uint32_t>(best)));
+      const float mn = fmaxf(m, fmaxf(t0m, t1m));
       l *= ex2_approx((m - mn) * kLog2e);
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      if (all_visible) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          a0 += ex2_approx((score(va[i]) - mn) * kLog2e);
-          a1 += ex2_approx((score(va[i + 1]) - mn) * kLog2e);
-          a2 += ex2_approx((score(vb[i]) - mn) * kLog2e);
-          a3 += ex2_approx((score(vb[i + 1]) - mn) * kLog2e);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          if (c0 + i <= lim) a0 += ex2_approx((score(va[i]) - mn) * kLog2e);
-          if (c0 + i + 1 <= lim) a1 += ex2_approx((score(va[i + 1]) - mn) * kLog2e);
-          if (c0 + 32 + i <= lim) a2 += ex2_approx((score(vb[i]) - mn) * kLog2e);
-          if (c0 + 33 + i <= lim) a3 += ex2_approx((score(vb[i + 1]) - mn) * kLog2e);
-        }
+      for (int i = 0; i < 32; i += 2) {  // masked keys: 2^(-inf) = 0
+        a0 += ex2_approx((__uint_as_float(va[i]) - mn) * kLog2e);
+        a1 += ex2_approx((__uint_as_float(va[i + 1]) - mn) * kLog2e);
+        a2 += ex2_approx((__uint_as_float(vb[i]) - mn) * kLog2e);
+        a3 += ex2_approx((__uint_as_float(vb[i + 1]) - mn) * kLog2e);
       }
       l += (a0 + a1) + (a2 + a3);
       m = mn;
@@ -355,28 +348,15 @@ attention_prefill_s8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       const int c0 = j * TILE_ROWS + half * 64;
       const bool all_visible = c0 + 63 <= t0 + p.past;
       uint32_t w[16];
-      auto prob = [&](uint32_t acc) {
-        const float e = expf(score(acc) - m);
+      to_scores(c0, all_visible);
+      auto prob = [&](uint32_t sbits) {  // a masked key has score -FLT_MAX: expf gives 0, the probability is 0
+        const float e = expf(__uint_as_float(sbits) - m);
         return __float2int_rn(__fmul_rn(div_by_row_sum(e, l, rl), 127.f));
       };
-      if (all_visible) {
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          w[q4] = pack_sat_s8x4(prob(va[q4 * 4]), prob(va[q4 * 4 + 1]), prob(va[q4 * 4 + 2]), prob(va[q4 * 4 + 3]));
-          w[8 + q4] = pack_sat_s8x4(prob(vb[q4 * 4]), prob(vb[q4 * 4 + 1]), prob(vb[q4 * 4 + 2]), prob(vb[q4 * 4 + 3]));
-        }
-      } else {
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          int x[4], y[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            x[i] = (c0 + q4 * 4 + i <= lim) ? prob(va[q4 * 4 + i]) : 0;
-            y[i] = (c0 + 32 + q4 * 4 + i <= lim) ? prob(vb[q4 * 4 + i]) : 0;
-          }
-          w[q4] = pack_sat_s8x4(x[0], x[1], x[2], x[3]);
-          w[8 + q4] = pack_sat_s8x4(y[0], y[1], y[2], y[3]);
-        }
+      for (int q4 = 0; q4 < 8; ++q4) {
+        w[q4] = pack_sat_s8x4(prob(va[q4 * 4]), prob(va[q4 * 4 + 1]), prob(va[q4 * 4 + 2]), prob(va[q4 * 4 + 3]));
+        w[8 + q4] = pack_sat_s8x4(prob(vb[q4 * 4]), prob(vb[q4 * 4 + 1]), prob(vb[q4 * 4 + 2]), prob(vb[q4 * 4 + 3]));
       }
       // P_{j-1} has been consumed by its MMAs (the first wait passes at once)
       ok = mbar_wait_status(smem_u32(p_empty), (j & 1) ^ 1, abort_flag, p.status, TI_ERR_ATT_P_EMPTY);
