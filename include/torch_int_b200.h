@@ -324,9 +324,16 @@ int ti_set_group_m(int tiles);
 /* Small-M GEMMs (M <= 128: decode steps) are launched with programmatic stream serialisation by default:
  * their CTAs may become resident while the kernel before them in the stream drains and fetch their first
  * weight tiles (model constants that no kernel writes); activations, outputs and scratch are touched only after
- * the earlier kernel has completed.  A caller that overwrites WEIGHTS with a kernel on the same stream right
- * before such a GEMM turns this off (on = 0).  No reference counterpart. */
+ * the earlier kernel has completed.  The LayerNorm-quantise kernels on at most 32 rows are launched the same
+ * way: they pull gamma, beta and the bias (constants as well) toward L2 and then wait.  A caller that
+ * overwrites WEIGHTS or LayerNorm parameters with a kernel on the same stream right before such a call turns
+ * this off (on = 0).  No reference counterpart. */
 int ti_set_dependent_launch(int on);
+
+/* GEMMs of at most 16 rows (decode steps) stage 16 rows of A per pipeline stage instead of the tile's 128
+ * (default on = 1): the shared memory this frees holds more weight tiles in flight.  Results are identical.
+ * No reference counterpart. */
+int ti_set_narrow_a(int on);
 
 /* ABI version of this header (bumped on incompatible changes). */
 int ti_abi_version(void);

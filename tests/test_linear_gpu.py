@@ -182,7 +182,8 @@ def test_rejects_bad_arguments(cuda_ops):
     assert C.linear_a8_w8_b8_o8(x[:0], w, b, 1.0, 1.0).shape == (0, 16)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 7168, 7168), (8, 21504, 7168), (16, 1040, 28672), (128, 4096, 4096), (3, 48, 2048)])
+@pytest.mark.parametrize("m,n,k", [(1, 7168, 7168), (8, 21504, 7168), (16, 1040, 28672), (128, 4096, 4096), (3, 48, 2048),
+                                   (8, 50272, 2048), (5, 4112, 2064)])
 def test_split_k_small_m(cuda_ops, m, n, k):
     """Few rows, long K (decode steps): K is split over the SMs, partial sums meet in a scratch
     workspace, the last CTA of a tile applies the epilogue.  Results must not change, twice in a row
@@ -193,6 +194,19 @@ def test_split_k_small_m(cuda_ops, m, n, k):
     alpha = 1.0 / (60.0 * k ** 0.5)
     for _ in range(2):
         run_all(C, x, w, b8, b32, bf, alpha, 0.01, f"split-K {m}x{n}x{k}")
+    C.set_narrow_a(0)  # the 128-row A stages that problems of more than 16 rows use
+    try:
+        out = torch.empty((m, n), dtype=torch.int8, device="cuda")
+        C.gemm_i8_ex(x.cuda(), w.cuda(), out, b8.cuda(), epilogue=C.EPI_S8_BIAS_S8, m=m, n=n, k=k,
+                     lda=k, ldb=k, ldc=n, alpha=alpha, beta=0.01)
+    finally:
+        C.set_narrow_a(1)
+    assert_bit_exact(out, O.linear_a8_w8_b8_o8(x, w, b8, alpha, 0.01), "128-row A stages")
+    for tile_n in (64, 128, 256):  # 64 has no narrow form
+        out = torch.empty((m, n), dtype=torch.int8, device="cuda")
+        C.gemm_i8_ex(x.cuda(), w.cuda(), out, b8.cuda(), epilogue=C.EPI_S8_BIAS_S8, m=m, n=n, k=k,
+                     lda=k, ldb=k, ldc=n, alpha=alpha, beta=0.01, tile_n=tile_n, cta_pair=1)
+        assert_bit_exact(out, O.linear_a8_w8_b8_o8(x, w, b8, alpha, 0.01), f"tile_n={tile_n}")
     for splits in (1, 2, 5, 16):
         out = torch.empty((m, n), dtype=torch.int8, device="cuda")
         C.gemm_i8_ex(x.cuda(), w.cuda(), out, b8.cuda(), epilogue=C.EPI_S8_BIAS_S8, m=m, n=n, k=k,

@@ -311,6 +311,12 @@ int ti_set_sm_limit(int sms) {
 
 int ti_set_dependent_launch(int on) {
   set_dependent_launch(on);
+  set_row_dependent_launch(on);
+  return TI_OK;
+}
+
+int ti_set_narrow_a(int on) {
+  set_narrow_a(on);
   return TI_OK;
 }
 

@@ -73,6 +73,10 @@ void set_group_m(int tiles);
 // start fetching weights while the kernel before them drains.  0 turns that off.
 void set_dependent_launch(int on);
 
+// Problems of at most 16 rows stage 16 rows of A per pipeline stage instead of 128 (default on), which
+// leaves room for half as many more weight bytes in flight per SM.  0: the 128-row stages.
+void set_narrow_a(int on);
+
 // Tensor map (CUtensorMap, 128 bytes, passed as an opaque pointer so that this header needs no
 // driver API types) of a K-major int8 operand [batch2, batch, rows, K]: box = 128 bytes of K x
 // box_rows x 1 x 1, 128-byte swizzle, out-of-range elements read as zero.  A batch index of extent

@@ -79,27 +79,37 @@ struct KernelParams {
 //               CTAs' shared memory and write 128 accumulator rows into each
 //               CTA's TMEM.  Per CTA this halves the B bytes that TMA writes to
 //               and the tensor core reads from shared memory.
-template <int BN, bool PAIR>
+// AROWS = rows of A that a stage holds.  128 is the tile height.  16 serves problems of at most 16 rows
+// (decode steps): the TMA box of A is 16 rows, so a stage is 2 KB + the B tile instead of 16 KB + the B
+// tile, and half as many more weight bytes are in flight per SM.  The MMA is still 128 rows high: rows 16
+// and up of its A operand are whatever follows in shared memory (the stage's own B tile), which gives
+// arbitrary integers in accumulator rows that no epilogue reads.
+template <int BN, bool PAIR, int AROWS = BM>
 struct Cfg {
-  static constexpr int A_BYTES = BM * BK;
+  static constexpr int A_BYTES = AROWS * BK;
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
   static constexpr int B_BYTES = B_ROWS * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int XPOSE_BYTES = 16 + 4 * 32 * 144;  // flag word + per epilogue warp: 32 rows x (128 + 16) bytes
+  // flag word + per epilogue warp with valid rows: 32 rows x (128 + 16) bytes
+  static constexpr int XPOSE_BYTES = 16 + (AROWS > 32 ? 4 : 1) * 32 * 144;
   static constexpr int AUX_BYTES = 4 * BN * 4 + 256 + XPOSE_BYTES;  // bias + alpha tiles, barriers, store staging
   static constexpr int STAGES_RAW = (SMEM_BUDGET - 1024 - AUX_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int TILE_M = PAIR ? 2 * BM : BM;
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32..256, multiple of 32");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
   static_assert(STAGES >= 2, "need at least two stages");
+  static_assert(AROWS == BM || (!PAIR && AROWS == 16 && B_BYTES >= BM * BK - A_BYTES),
+                "a narrow A stage needs a B tile behind it that covers the MMA's 128-row read");
+  static_assert((2 * STAGES + 4) * 8 + 8 <= 256, "barrier area");
 };
 
 struct TileCoord {
   int m_tile, n_tile, b1, b2;
   int kb0, kb1;  // K blocks [kb0, kb1) of this work item
+  int parts;     // work items that share this tile (1: this one computes all of it)
 };
 
 __device__ __forceinline__ TileCoord decode_tile(long long t, const KernelParams& p) {
@@ -127,8 +137,21 @@ __device__ __forceinline__ TileCoord decode_tile(long long t, const KernelParams
   c.n_tile = r / gm;
   c.kb0 = kb0;
   c.kb1 = kb1;
+  c.parts = p.splits;
   return c;
 }
+
+// The work items of one CTA (or CTA pair), in order: every warp role walks the same sequence.
+struct WorkIter {
+  long long t, step;
+  __device__ WorkIter(long long first, long long stride) : t(first), step(stride) {}
+  __device__ bool next(const KernelParams& p, TileCoord& c) {
+    if (t >= p.total_tiles) return false;
+    c = decode_tile(t, p);
+    t += step;
+    return true;
+  }
+};
 
 // Fire-and-forget integer add to global memory: `red` returns nothing, so a thread keeps issuing
 // the next ones while these are on their way to L2.
@@ -185,11 +208,11 @@ __device__ __forceinline__ uint32_t epilogue_one(uint32_t acc_bits, uint32_t t, 
   }
 }
 
-template <int BN, int EPI, bool PAIR>
+template <int BN, int EPI, bool PAIR, int AROWS = BM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const KernelParams p) {
-  using C = Cfg<BN, PAIR>;
+  using C = Cfg<BN, PAIR, AROWS>;
   using T = EpiTraits<EPI>;
   constexpr int CG = PAIR ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
@@ -247,35 +270,45 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int prefetched = 0;  // K blocks of the first work item whose stages were filled before the loop
+      int prefetched = 0;  // K blocks (over the first work items) whose stages were filled before the loop
+      WorkIter work(first_tile, tile_step);
       if constexpr (!PAIR) {
-        if (p.pdl && first_tile < p.total_tiles) {
-          // weights first: they do not depend on the kernel before this one
-          const TileCoord tc = decode_tile(first_tile, p);
-          const int row_a = tc.m_tile * C::TILE_M;
-          const int row_b = tc.n_tile * BN;
-          const int n = min(C::STAGES, tc.kb1 - tc.kb0);
-          for (int s = 0; s < n; ++s) {
-            const uint32_t fb = smem_u32(&full_bar[s]);
-            mbar_expect_tx(fb, C::STAGE_BYTES);
-            tma_load_4d(smem_u32(smem + s * C::STAGE_BYTES + C::A_BYTES), &tmap_b, fb, (tc.kb0 + s) * BK, row_b,
-                        tc.b1 * p.b_b1, tc.b2 * p.b_b2);
+        if (p.pdl) {
+          // Weights of the first K blocks of this CTA's work first: they do not depend on the kernel before
+          // this one.  The activations follow once that kernel has completed.
+          int a_kb[C::STAGES], a_b1[C::STAGES], a_b2[C::STAGES];
+          int n = 0;
+          {
+            WorkIter ahead = work;
+            TileCoord c;
+            while (n < C::STAGES && ahead.next(p, c)) {
+              for (int kb = c.kb0; kb < c.kb1 && n < C::STAGES; ++kb, ++n) {
+                const uint32_t fb = smem_u32(&full_bar[n]);
+                mbar_expect_tx(fb, C::STAGE_BYTES);
+                tma_load_4d(smem_u32(smem + n * C::STAGE_BYTES + C::A_BYTES), &tmap_b, fb, kb * BK, c.n_tile * BN,
+                            c.b1 * p.b_b1, c.b2 * p.b_b2);
+                a_kb[n] = kb;
+                a_b1[n] = c.b1 * p.a_b1;
+                a_b2[n] = c.b2 * p.a_b2;
+              }
+            }
           }
-          grid_dep_wait();  // the activations are the output of the kernel before
-          for (int s = 0; s < n; ++s)
-            tma_load_4d(smem_u32(smem + s * C::STAGE_BYTES), &tmap_a, smem_u32(&full_bar[s]), (tc.kb0 + s) * BK, row_a,
-                        tc.b1 * p.a_b1, tc.b2 * p.a_b2);
+          grid_dep_wait();
+          for (int i = 0; i < n; ++i)  // one M tile (M <= 128): row 0
+            tma_load_4d(smem_u32(smem + i * C::STAGE_BYTES), &tmap_a, smem_u32(&full_bar[i]), a_kb[i] * BK, 0, a_b1[i],
+                        a_b2[i]);
           prefetched = n;
           stage = n == C::STAGES ? 0 : n;
           phase = n == C::STAGES ? 1 : 0;
         }
       }
-      for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step) {
-        const TileCoord tc = decode_tile(t, p);
+      TileCoord tc;
+      while (ok && work.next(p, tc)) {
         const int row_a = tc.m_tile * C::TILE_M + static_cast<int>(rank) * BM;
         const int row_b = tc.n_tile * BN + static_cast<int>(rank) * C::B_ROWS;
-        const int kb_first = tc.kb0 + prefetched;
-        prefetched = 0;
+        const int skip = min(prefetched, tc.kb1 - tc.kb0);
+        prefetched -= skip;
+        const int kb_first = tc.kb0 + skip;
         for (int kb = kb_first; kb < tc.kb1; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, TI_ERR_WAIT_EMPTY);
           if (!ok) break;
@@ -314,13 +347,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
+      WorkIter work(first_tile, tile_step);
+      TileCoord tc;
+      for (; ok && work.next(p, tc); ++it) {
         const int buf = it & 1;
-        int kb0 = 0, kb1 = p.num_kb;
-        if (p.splits > 1) {
-          kb0 = static_cast<int>(t % p.splits) * p.kb_per_split;
-          kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        }
+        const int kb0 = tc.kb0, kb1 = tc.kb1;
         ok = mbar_wait<PAIR>(smem_u32(&tempty_bar[buf]), ((it >> 1) & 1) ^ 1, abort_flag,
                              TI_ERR_WAIT_TMEM_EMPTY);
         if (!ok) break;
@@ -366,8 +397,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int et = threadIdx.x - 64;
     int it = 0;
     bool ok = true;
-    for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
-      const TileCoord tc = decode_tile(t, p);
+    WorkIter work(first_tile, tile_step);
+    TileCoord tc;
+    for (; ok && work.next(p, tc); ++it) {
       const int buf = it & 1;
       const int n0 = tc.n_tile * BN;
       if constexpr (T::kHasBias) {
@@ -412,7 +444,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       };
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       const uint32_t* bs = bias_smem + buf * BN;
-      if (p.splits > 1) {
+      if (tc.parts > 1) {
         // ---- split-K: add this work item's partial sums into the workspace ----
         // Rows are transposed through the warp's shared-memory patch so that lane L adds column L of
         // every valid row: each warp-wide reduction touches 128 contiguous bytes of the workspace.
@@ -420,7 +452,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint8_t* patch = xpose + 16 + quarter * (32 * 144);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          if (n0 + c * 32 >= p.N) break;
+          if (n0 + c * 32 >= p.N || valid <= 0) break;
           uint32_t v[32];
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, v);
@@ -449,7 +481,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         if (et == 0) {
           const int old = atomicAdd(p.counters + tc.n_tile, 1);
-          *reinterpret_cast<volatile int*>(xpose) = (old == p.splits - 1) ? 1 : 0;
+          *reinterpret_cast<volatile int*>(xpose) = (old == tc.parts - 1) ? 1 : 0;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         const bool last = *reinterpret_cast<volatile int*>(xpose) != 0;
@@ -495,7 +527,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint8_t* crow = row_ptr(row_ok ? row : 0);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          if (n0 + c * 32 >= p.N) break;  // uniform over the CTA
+          if (n0 + c * 32 >= p.N || row0 >= p.M) break;  // uniform over the warp
           uint32_t v[32];
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, v);
@@ -544,6 +576,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           if (n0 + c * 32 >= p.N) break;  // uniform over the CTA
+          if (row0 >= p.M) break;  // no valid row in this warp (its patch may not exist: narrow A stages)
           uint32_t v[32];
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, v);
@@ -674,6 +707,8 @@ int g_sm_limit = 0;
 int g_group_m = 0;
 // Small-M launches use programmatic dependent launch (1) or ordinary stream order (0).
 int g_pdl = 1;
+// Problems of at most 16 rows use 16-row A stages (1) or the full 128-row ones (0).
+int g_narrow_a = 1;
 
 int num_sms() {
   static int cached[64] = {0};
@@ -697,14 +732,14 @@ int64_t counter_bytes(int bn, int64_t N) {
   return (tiles * 4 + 255) / 256 * 256;
 }
 
-template <int BN, int EPI, bool PAIR>
+template <int BN, int EPI, bool PAIR, int AROWS = BM>
 int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
-  using C = Cfg<BN, PAIR>;
+  using C = Cfg<BN, PAIR, AROWS>;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI, PAIR>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI, PAIR, AROWS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
@@ -713,7 +748,7 @@ int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
     attr_done[dev] = true;
   }
   CUtensorMap ta, tb;
-  if (!make_operand_map(&ta, g.A, g.K, g.M, g.batch, g.batch2, g.lda, g.strideA, g.stride2A, BM))
+  if (!make_operand_map(&ta, g.A, g.K, g.M, g.batch, g.batch2, g.lda, g.strideA, g.stride2A, AROWS))
     return TI_E_CUDA;
   if (!make_operand_map(&tb, g.B, g.K, g.N, g.batch, g.batch2, g.ldb, g.strideB, g.stride2B, C::B_ROWS))
     return TI_E_CUDA;
@@ -786,7 +821,7 @@ int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_kernel<BN, EPI, PAIR>, ta, tb, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_kernel<BN, EPI, PAIR, AROWS>, ta, tb, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     set_error("gemm_i8_kernel<%d,%d,%d> launch failed: %s", BN, EPI, PAIR ? 1 : 0, cudaGetErrorString(e));
@@ -798,6 +833,10 @@ int launch_one(const GemmProblem& g, int splits, cudaStream_t stream) {
 template <int EPI>
 int launch_bn(const GemmProblem& g, int bn, bool pair, int splits, cudaStream_t stream) {
   if (pair) return launch_one<256, EPI, true>(g, 1, stream);
+  if (g_narrow_a && g.M <= 16) {  // decode steps: narrow A stages, deeper weight pipeline
+    if (bn == 256) return launch_one<256, EPI, false, 16>(g, splits, stream);
+    if (bn == 128) return launch_one<128, EPI, false, 16>(g, splits, stream);
+  }
   switch (bn) {
     case 256: return launch_one<256, EPI, false>(g, splits, stream);
     case 128: return launch_one<128, EPI, false>(g, splits, stream);
@@ -1088,6 +1127,8 @@ void set_sm_limit(int sms) { g_sm_limit = sms > 0 ? sms : 0; }
 void set_group_m(int tiles) { g_group_m = tiles > 0 ? tiles : 0; }
 
 void set_dependent_launch(int on) { g_pdl = on ? 1 : 0; }
+
+void set_narrow_a(int on) { g_narrow_a = on ? 1 : 0; }
 
 // Reads (and optionally clears) the status word the kernels of this file set
 // when a bounded wait gives up.  Synchronises the device.

@@ -139,6 +139,26 @@ __device__ __forceinline__ void layernorm_quant_row(float4 (&x)[VPT], int h4, co
   }
 }
 
+// Start of a row kernel inside a chain of dependent launches (decode steps).  The small-M GEMM that follows
+// may be scheduled at once and fetch its weights while this kernel runs.  dep != 0: this kernel was itself
+// launched as a programmatic dependent of the GEMM before it, so its launch latency overlaps that GEMM's last
+// CTAs; it pulls its per-layer parameters (which no kernel writes) toward L2 before it waits for the GEMM.
+// Measured on the OPT-30B decode step: 8.02-8.08 ms with dep = 0, 7.84-7.89 ms with dep = 1 (7.96 ms when the
+// next GEMM is let go only after the wait).
+template <int THREADS>
+__device__ __forceinline__ void row_kernel_prologue(int dep, int H, const float* gamma, const float* beta,
+                                                    const float* bias) {
+  grid_dep_launch();
+  if (dep != 0) {
+    for (int line = threadIdx.x; line * 32 < H; line += THREADS) {  // 128-byte lines of H floats
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(gamma + line * 32));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(beta + line * 32));
+      if (bias != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(bias + line * 32));
+    }
+  }
+  grid_dep_wait();  // this kernel reads the output of the one before it
+}
+
 // T: storage type of x.  LN: float = the LayerNorm output stays fp32 (the reference's LayerNormQ with
 // fp32 parameters casts x to fp32 first, nn/fused.py:14); __half = it is rounded to fp16 before
 // quantising (parameters cast to fp16 as well).
@@ -146,10 +166,9 @@ template <typename T, typename LN, int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 layernorm_q_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                    const float* __restrict__ beta, float eps, int8_t* __restrict__ q, int H,
-                   long long ldx, long long ldq) {
+                   long long ldx, long long ldq, int dep) {
   __shared__ float scratch[32];
-  grid_dep_launch();  // a small-M GEMM that follows may start fetching its weights now ...
-  grid_dep_wait();    // ... and this kernel reads the output of the one before it
+  row_kernel_prologue<THREADS>(dep, H, gamma, beta, nullptr);
   const long long row = blockIdx.x;
   const int h4 = H >> 2;
   const T* xr = x + row * ldx;
@@ -167,10 +186,9 @@ __global__ void __launch_bounds__(THREADS)
 dq_add_layernorm_q_kernel(const int32_t* __restrict__ in, float scale, const T* __restrict__ res,
                           const float* __restrict__ in_bias, const float* __restrict__ gamma,
                           const float* __restrict__ beta, float eps, T* __restrict__ res_out,
-                          int8_t* __restrict__ q, int H) {
+                          int8_t* __restrict__ q, int H, int dep) {
   __shared__ float scratch[32];
-  grid_dep_launch();  // a small-M GEMM that follows may start fetching its weights now ...
-  grid_dep_wait();    // ... and this kernel reads the output of the one before it
+  row_kernel_prologue<THREADS>(dep, H, gamma, beta, in_bias);
   const long long row = blockIdx.x;
   const int h4 = H >> 2;
   const int32_t* ir = in + row * H;
@@ -725,6 +743,26 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
     default: { constexpr int VPT = 16; __VA_ARGS__; break; }          \
   }
 
+// 1: a row kernel on at most kRowDepMaxRows rows (decode steps) is launched as a programmatic dependent of the
+// kernel before it (see row_kernel_prologue).
+int g_row_dep_mode = 1;
+constexpr int64_t kRowDepMaxRows = 32;
+
+template <typename... KArgs, typename... Args>
+void launch_row_kernel(void (*kernel)(KArgs...), unsigned grid, unsigned threads, cudaStream_t stream, bool dependent,
+                       Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T, typename LN>
 int layernorm_q_typed(const T* x, const float* gamma, const float* beta, float eps, int8_t* q,
                       int64_t rows, int64_t H, cudaStream_t stream) {
@@ -737,16 +775,17 @@ int layernorm_q_typed(const T* x, const float* gamma, const float* beta, float e
       layernorm_q_generic_kernel<T, LN, false><<<grid, 256, 0, stream>>>(
           x, nullptr, 0.f, nullptr, gamma, beta, eps, nullptr, q, static_cast<int>(H), H, H);
     });
+  const int dep = rows <= kRowDepMaxRows ? g_row_dep_mode : 0;
   if (h4 <= 128)
     return check_launch("layernorm_q", [&] {
-      layernorm_q_kernel<T, LN, 128, 1><<<grid, 128, 0, stream>>>(x, gamma, beta, eps, q,
-                                                                  static_cast<int>(H), H, H);
+      launch_row_kernel(layernorm_q_kernel<T, LN, 128, 1>, grid, 128, stream, dep != 0, x, gamma, beta, eps, q,
+                        static_cast<int>(H), H, H, dep);
     });
   const int vpt = (h4 + 255) / 256;
   int rc = TI_OK;
   TI_VPT_SWITCH(vpt, rc = check_launch("layernorm_q", [&] {
-                  layernorm_q_kernel<T, LN, 256, VPT><<<grid, 256, 0, stream>>>(
-                      x, gamma, beta, eps, q, static_cast<int>(H), H, H);
+                  launch_row_kernel(layernorm_q_kernel<T, LN, 256, VPT>, grid, 256, stream, dep != 0, x, gamma, beta,
+                                    eps, q, static_cast<int>(H), H, H, dep);
                 }));
   return rc;
 }
@@ -766,21 +805,24 @@ int dq_add_layernorm_q_typed(const int32_t* in, float scale, const T* res, const
       layernorm_q_generic_kernel<T, T, true><<<grid, 256, 0, stream>>>(
           res, in, scale, in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H), H, H);
     });
+  const int dep = rows <= kRowDepMaxRows ? g_row_dep_mode : 0;
   if (h4 <= 128)
     return check_launch("dq_add_layernorm_q", [&] {
-      dq_add_layernorm_q_kernel<T, 128, 1><<<grid, 128, 0, stream>>>(
-          in, scale, res, in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H));
+      launch_row_kernel(dq_add_layernorm_q_kernel<T, 128, 1>, grid, 128, stream, dep != 0, in, scale, res, in_bias,
+                        gamma, beta, eps, res_out, q, static_cast<int>(H), dep);
     });
   const int vpt = (h4 + 255) / 256;
   int rc = TI_OK;
   TI_VPT_SWITCH(vpt, rc = check_launch("dq_add_layernorm_q", [&] {
-                  dq_add_layernorm_q_kernel<T, 256, VPT><<<grid, 256, 0, stream>>>(
-                      in, scale, res, in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H));
+                  launch_row_kernel(dq_add_layernorm_q_kernel<T, 256, VPT>, grid, 256, stream, dep != 0, in, scale, res,
+                                    in_bias, gamma, beta, eps, res_out, q, static_cast<int>(H), dep);
                 }));
   return rc;
 }
 
 }  // namespace
+
+void set_row_dependent_launch(int on) { g_row_dep_mode = on ? 1 : 0; }
 
 int layernorm_q(const void* x, int x_is_half, const float* gamma, const float* beta, float eps,
                 int8_t* q, int64_t rows, int64_t H, cudaStream_t stream) {

@@ -7,6 +7,11 @@
 
 namespace ti {
 
+// Row kernels on at most 32 rows (decode steps) are launched as programmatic dependents of the kernel before
+// them (default on): their launch latency overlaps that kernel's last CTAs and they pull their per-layer
+// parameters toward L2 before they wait for it.
+void set_row_dependent_launch(int on);
+
 int layernorm_q(const void* x, int x_is_half, const float* gamma, const float* beta, float eps,
                 int8_t* q, int64_t rows, int64_t H, cudaStream_t stream);
 

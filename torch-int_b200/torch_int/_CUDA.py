@@ -114,6 +114,7 @@ _c_abi_version = _sig("ti_abi_version", [])
 _c_set_sm_limit = _sig("ti_set_sm_limit", [_i32])
 _c_set_group_m = _sig("ti_set_group_m", [_i32])
 _c_set_dependent_launch = _sig("ti_set_dependent_launch", [_i32])
+_c_set_narrow_a = _sig("ti_set_narrow_a", [_i32])
 
 if _c_abi_version() != 1:
     raise ImportError("torch_int._CUDA: libtorch_int_b200.so has an unexpected ABI version")
@@ -613,6 +614,11 @@ def transpose_values(v, vt, col0=0):
 def set_dependent_launch(on):
     """Programmatic dependent launch of the small-M GEMMs on (default) or off; see ti_set_dependent_launch."""
     _c_set_dependent_launch(1 if on else 0)
+
+
+def set_narrow_a(on):
+    """16-row A stages for GEMMs of at most 16 rows on (default) or off; see ti_set_narrow_a."""
+    _c_set_narrow_a(1 if on else 0)
 
 
 def set_group_m(tiles):
