@@ -52,8 +52,15 @@ __device__ __forceinline__ int warp_sum_i(int v) {
 constexpr int DEC_THREADS = 256;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 
+// Loads a thread keeps in flight in the score loop (key rows) and in the context loop (value rows).  The
+// kernel is bound by memory latency: a (sequence, head) pair holds 2 x S x D bytes and every pass over
+// them costs one round trip.  Four CTAs must fit an SM (64 registers per thread): batch x heads = 448 CTAs
+// of the OPT-30B decode step then run as one wave on 148 SMs.
+constexpr int DEC_KEYS_IN_FLIGHT = 8;
+constexpr int DEC_VALUE_ROWS_IN_FLIGHT = 8;
+
 template <int D>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, 4)
 decode_attention_s8_kernel(const int8_t* __restrict__ qkv, long long ld_qkv, int8_t* __restrict__ keys,
                            int8_t* __restrict__ values_t, int cap, int hl, const int* __restrict__ pos,
                            float alpha_qk, float alpha_pv, int8_t* __restrict__ ctx, long long ld_ctx,
@@ -89,18 +96,19 @@ decode_attention_s8_kernel(const int8_t* __restrict__ qkv, long long ld_qkv, int
   const uint4 qp = reinterpret_cast<const uint4*>(qrow)[piece];
   __syncthreads();  // the new key row and value column are visible to the whole CTA
 
-  // ---- scores: PIECES lanes share a key row (one coalesced row per load), four rows in flight per lane
+  // ---- scores: PIECES lanes share a key row (one coalesced row per load), KU rows in flight per lane
+  constexpr int KU = DEC_KEYS_IN_FLIGHT;
   float mx = -FLT_MAX;
-  for (int base = warp * RPW * 4; base < S; base += DEC_WARPS * RPW * 4) {
-    uint4 kv[4];
+  for (int base = warp * RPW * KU; base < S; base += DEC_WARPS * RPW * KU) {
+    uint4 kv[KU];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < KU; ++u) {
       const int j = base + u * RPW + sub;
       kv[u] = j < S ? reinterpret_cast<const uint4*>(krows + static_cast<long long>(j) * el)[piece]
                     : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < KU; ++u) {
       int acc = dot16(qp, kv[u], 0);
 #pragma unroll
       for (int o = 1; o < PIECES; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -137,23 +145,31 @@ decode_attention_s8_kernel(const int8_t* __restrict__ qkv, long long ld_qkv, int
   }
   __syncthreads();
 
-  // ---- context: a warp owns D/8 value rows and takes four at a time; lanes stride over the
+  // ---- context: a warp owns D/8 value rows and takes VU at a time; lanes stride over the
   //      positions 16 bytes at a time (one coalesced 512-byte segment of a row per load)
   constexpr int ROWS = D / DEC_WARPS;
+  constexpr int VU = ROWS < DEC_VALUE_ROWS_IN_FLIGHT ? ROWS : DEC_VALUE_ROWS_IN_FLIGHT;
 #pragma unroll 1
-  for (int dd = 0; dd < ROWS; dd += 4) {
+  for (int dd = 0; dd < ROWS; dd += VU) {
     const int d0 = warp * ROWS + dd;
-    int acc[4] = {0, 0, 0, 0};
+    int acc[VU];
+#pragma unroll
+    for (int u = 0; u < VU; ++u) acc[u] = 0;
     for (int j = lane * 16; j < s_pad; j += 512) {
       const uint4 pp = *reinterpret_cast<const uint4*>(s_probs + j);
+      uint4 vv[VU];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        acc[u] = dot16(pp, *reinterpret_cast<const uint4*>(vrows + static_cast<long long>(d0 + u) * cap + j), acc[u]);
+      for (int u = 0; u < VU; ++u)
+        vv[u] = *reinterpret_cast<const uint4*>(vrows + static_cast<long long>(d0 + u) * cap + j);
+#pragma unroll
+      for (int u = 0; u < VU; ++u) acc[u] = dot16(pp, vv[u], acc[u]);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] = warp_sum_i(acc[u]);
-    if (lane < 4) {
-      const int a = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+    for (int u = 0; u < VU; ++u) acc[u] = warp_sum_i(acc[u]);
+    int a = acc[0];
+#pragma unroll
+    for (int u = 1; u < VU; ++u) a = lane == u ? acc[u] : a;
+    if (lane < VU) {
       const int o = max(-128, min(127, __float2int_rn(alpha_pv * __int2float_rn(a))));
       ctx[b * ld_ctx + h * D + d0 + lane] = static_cast<int8_t>(o);
     }
