@@ -437,8 +437,17 @@ class OptWorkload:
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / (steps - 3)
         wbytes = sum(b.numel() for n, b in model.named_buffers() if b.dtype == torch.int8)
+        # everything a step has to read from HBM: the int8 weights, the fp16 lm_head table (this rank's rows
+        # when the head is vocabulary-parallel) and the cached keys and values at the mean length of the timed steps
+        attn = model.model.decoder.layers[0].self_attn
+        head = model.lm_head.weight
+        head_rows = head.shape[0] // self.world if (self.world > 1 and self.tp.vocab_parallel) else head.shape[0]
+        mean_len = self.seq + 3 + (steps - 2) / 2.0  # positions a timed step attends to, first to last
+        kv_bytes = 2 * self.batch * attn.local_heads * attn.head_dim * mean_len * len(model.model.decoder.layers)
+        hbm_bytes = wbytes + head_rows * head.shape[1] * head.element_size() + kv_bytes
         return {"decode_tokens_per_s": round(self.batch / (ms * 1e-3), 1), "decode_ms_per_step": round(ms, 3),
                 "decode_steps_timed": steps - 3, "decode_weight_gb_per_s_per_gpu": round(wbytes / (ms * 1e-3) / 1e9, 1),
+                "decode_hbm_gb_per_s_per_gpu": round(hbm_bytes / (ms * 1e-3) / 1e9, 1),
                 "decode_mode": "CUDA graph replay" if graph is not None else "eager launches"}
 
     def cpu_sample(self):
