@@ -112,8 +112,11 @@ enum ti_epilogue {
   TI_EPI_F32_ALPHA = 5,      /* ti_bmm_s8t_s8n_f32t */
   TI_EPI_S8_ALPHA = 6,       /* ti_bmm_s8t_s8n_s8t */
   TI_EPI_S32_RAW = 7,        /* ti_bmm_s8t_s8n_s32t */
-  TI_EPI_S8_BIAS_S8_VEC = 8  /* ti_linear_a8_w8_b8_o8 with per-column alpha[n], beta[n] (alpha_vec, beta_vec):
+  TI_EPI_S8_BIAS_S8_VEC = 8, /* ti_linear_a8_w8_b8_o8 with per-column alpha[n], beta[n] (alpha_vec, beta_vec):
                                 several such linears that share their input, e.g. q/k/v, run as one GEMM */
+  TI_EPI_F32_BIAS_F32_ACC = 9 /* C (fp32) += fma(alpha, acc, beta * bias): ti_linear_a8_w8_bfp32_ofp32 followed by the
+                                in-place residual add of Int8OPTDecoderLayer (torch_int/models/opt.py:281,289:
+                                residual.add_(hidden_states)), in the epilogue; C is read and written */
 };
 
 /* A [batch2][batch][M][K], B [batch2][batch][N][K], C [batch2][batch][M][N];

@@ -14,7 +14,8 @@ import torch
 from oracle import w8a8 as O
 
 EPI_S8_BIAS_S8, EPI_S8_BIAS_S8_RELU, EPI_F32_BIAS_F32, EPI_S32_BIAS_S32_ADD, \
-    EPI_S32_BIAS_S32_SCALE, EPI_F32_ALPHA, EPI_S8_ALPHA, EPI_S32_RAW, EPI_S8_BIAS_S8_VEC = range(9)
+    EPI_S32_BIAS_S32_SCALE, EPI_F32_ALPHA, EPI_S8_ALPHA, EPI_S32_RAW, EPI_S8_BIAS_S8_VEC, \
+    EPI_F32_BIAS_F32_ACC = range(10)
 _KIND = {EPI_S8_BIAS_S8: "b8_o8", EPI_S8_BIAS_S8_RELU: "relu_b8_o8", EPI_F32_BIAS_F32: "bfp32_ofp32",
          EPI_S32_BIAS_S32_ADD: "b32_o32", EPI_S32_BIAS_S32_SCALE: "b32_o32_with_scaling",
          EPI_F32_ALPHA: "f32t", EPI_S8_ALPHA: "s8t", EPI_S32_RAW: "s32t"}
@@ -66,6 +67,8 @@ def gemm_i8_ex(a, b, out, bias=None, *, epilogue, m, n, k, batch=1, batch2=1, ld
                 y = (alpha_vec.numpy().astype(np.float64)[None, :] * f.astype(np.float64) +
                      t.astype(np.float64)[None, :]).astype(np.float32)
                 res = torch.from_numpy(np.clip(np.rint(y.astype(np.float64)), -128, 127).astype(np.int8))
+            elif epilogue == EPI_F32_BIAS_F32_ACC:  # the fp32 linear's output added to what C holds
+                res = cv[i2, i1] + O.epilogue_numpy(acc, bias, alpha, beta, "bfp32_ofp32")
             else:
                 res = O.epilogue_numpy(acc, bias, alpha, beta, _KIND[epilogue])
             cv[i2, i1].copy_(res)

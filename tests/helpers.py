@@ -46,6 +46,15 @@ def assert_quant_close(got, want, min_exact=0.999, what=""):
     assert exact >= min_exact, f"{what}: only {exact:.5f} of elements identical"
 
 
+def set_residual_in_gemm(model, on):
+    """Switches every decoder layer of `model` between adding the out_proj / fc2 outputs to the residual in
+    the GEMM epilogue and in the fused residual/LayerNorm row kernel (bit-identical results)."""
+    for m in model.modules():
+        if hasattr(m, "residual_in_gemm"):
+            m.residual_in_gemm = bool(on)
+    return model
+
+
 def set_fused_attention(model, on):
     """Switches every attention module of `model` between the one-kernel causal attention and the
     scores -> softmax_q -> context chain (the two agree except at rounding ties of a probability)."""

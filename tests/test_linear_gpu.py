@@ -215,3 +215,26 @@ def test_split_k_small_m(cuda_ops, m, n, k):
     ws = C._split_k_workspace(torch.device("cuda", torch.cuda.current_device()))
     assert int(ws.count_nonzero()) == 0, "the split-K workspace must be left zeroed"
     assert C.device_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 7168, 7168), (300, 1040, 528), (130, 48, 2048), (8, 7168, 7168), (1, 16, 16)])
+def test_fp32_epilogue_that_adds_to_c(cuda_ops, m, n, k):
+    """C += fma(alpha, acc, bias): the fp32-output linear with the residual add of the decoder layer folded into
+    its epilogue.  The sum must be exactly fp32(C + y) with y the value the plain fp32 epilogue stores."""
+    C = cuda_ops
+    x, w, bf = rand_s8((m, k), 61), rand_s8((n, k), 62), randn((n,), 63)
+    alpha = 1.0 / (60.0 * k ** 0.5)
+    start = randn((m, n), 64)
+    y = C.linear_a8_w8_bfp32_ofp32(x.cuda(), w.cuda(), bf.cuda(), alpha, 1.0)
+    assert_fp32_close(y, O.linear_a8_w8_bfp32_ofp32(x, w, bf, alpha, 1.0), 1e-5, "plain fp32 epilogue")
+    out = start.cuda()
+    C.gemm_i8_ex(x.cuda(), w.cuda(), out, bf.cuda(), epilogue=C.EPI_F32_BIAS_F32_ACC, m=m, n=n, k=k, lda=k, ldb=k,
+                 ldc=n, alpha=alpha, beta=1.0)
+    assert_bit_exact((start.cuda() + y).view(torch.int32), out.view(torch.int32), f"C += y at {m}x{n}x{k}")
+    wide = torch.full((m, n + 16), 7.0, device="cuda")   # a view into a wider tensor: the columns beyond N stay
+    wide[:, :n] = start.cuda()
+    C.gemm_i8_ex(x.cuda(), w.cuda(), wide, bf.cuda(), epilogue=C.EPI_F32_BIAS_F32_ACC, m=m, n=n, k=k, lda=k, ldb=k,
+                 ldc=n + 16, alpha=alpha, beta=1.0)
+    assert_bit_exact(wide[:, :n].contiguous().view(torch.int32), out.view(torch.int32), "strided C")
+    assert bool((wide[:, n:] == 7.0).all())
+    assert C.device_status() == 0

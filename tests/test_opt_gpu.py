@@ -3,7 +3,7 @@ restatement of the reference's dataflow (oracle/opt_model.py)."""
 import pytest
 import torch
 
-from helpers import assert_bit_exact, rand_s8, randn, set_fused_attention
+from helpers import assert_bit_exact, rand_s8, randn, set_fused_attention, set_residual_in_gemm
 from oracle import opt_model as OM
 from oracle import w8a8 as O
 
@@ -199,6 +199,34 @@ def test_causal_lm_logits(cuda_ops, seq):
         unfused = model(ids.cuda()).logits
         assert_bit_exact(ref_path.view(torch.int32), unfused.view(torch.int32), "reference-signature layers vs fused wiring")
         assert rel_err(unfused, logits) < 1e-2   # one-kernel attention: tie flips only
+
+
+def test_residual_added_in_the_gemm_epilogue(cuda_ops):
+    """Prefill with more than 128 tokens on one GPU adds the out_proj / fc2 outputs to the fp32 residual in the
+    GEMM epilogue.  Bit for bit the same logits as with the fused residual/LayerNorm row kernel, and as the
+    reference-signature layers."""
+    cfg, model = small_model()
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, cfg.vocab_size, (3, 96), generator=g).cuda()
+    set_fused_attention(model, False)
+    in_gemm = model(ids).logits
+    set_residual_in_gemm(model, False)
+    in_row_kernel = model(ids).logits
+    ref_path = model(ids, reference_path=True).logits
+    assert_bit_exact(in_gemm.view(torch.int32), in_row_kernel.view(torch.int32), "residual add in the GEMM epilogue")
+    assert_bit_exact(in_gemm.view(torch.int32), ref_path.view(torch.int32), "reference-signature layers")
+    set_fused_attention(model, True)
+    a = model(ids).logits
+    set_residual_in_gemm(model, True)
+    b = model(ids).logits
+    assert_bit_exact(a.view(torch.int32), b.view(torch.int32), "with the one-kernel attention")
+    cache = model.new_cache(3, 128)   # with a cache: prefill through the new path, then one decode step
+    out = model(ids, past_key_values=cache, use_cache=True, last_token_only=True)
+    set_residual_in_gemm(model, False)
+    cache2 = model.new_cache(3, 128)
+    out2 = model(ids, past_key_values=cache2, use_cache=True, last_token_only=True)
+    assert_bit_exact(out.logits.view(torch.int32), out2.logits.view(torch.int32), "prefill into a cache")
+    assert cuda_ops.device_status() == 0
 
 
 def test_fp16_residual_stream(cuda_ops):

@@ -21,6 +21,7 @@ enum Epilogue : int {
   EPI_S8_ALPHA,            // int8  out = sat_rne(alpha * a)
   EPI_S32_RAW,             // int32 out = acc
   EPI_S8_BIAS_S8_VEC,      // int8  out = sat_rne(fma(alpha[n], a, beta[n] * f32(bias[n]))): per-column scales
+  EPI_F32_BIAS_F32_ACC,    // fp32  out = out + y (C is read and added to),  bias fp32
   EPI_COUNT
 };
 

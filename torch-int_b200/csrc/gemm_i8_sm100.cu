@@ -175,7 +175,9 @@ struct EpiTraits {
       EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU || EPI == EPI_S8_ALPHA || EPI == EPI_S8_BIAS_S8_VEC;
   static constexpr bool kHasBias = EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU ||
                                    EPI == EPI_F32_BIAS_F32 || EPI == EPI_S32_BIAS_S32_ADD ||
-                                   EPI == EPI_S32_BIAS_S32_SCALE || EPI == EPI_S8_BIAS_S8_VEC;
+                                   EPI == EPI_S32_BIAS_S32_SCALE || EPI == EPI_S8_BIAS_S8_VEC ||
+                                   EPI == EPI_F32_BIAS_F32_ACC;
+  static constexpr bool kAddToC = EPI == EPI_F32_BIAS_F32_ACC;  // the fp32 result is added to what C holds
   static constexpr bool kVecAlpha = EPI == EPI_S8_BIAS_S8_VEC;
   static constexpr int kOutBytes = kOutS8 ? 1 : 4;
 };
@@ -413,7 +415,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               alpha_smem[buf * BN + j] = __float_as_uint(p.alpha_vec[n]);
             } else if constexpr (EPI == EPI_S8_BIAS_S8 || EPI == EPI_S8_BIAS_S8_RELU)
               v = __float_as_uint(p.beta * static_cast<float>(static_cast<const int8_t*>(p.bias)[n]));
-            else if constexpr (EPI == EPI_F32_BIAS_F32)
+            else if constexpr (EPI == EPI_F32_BIAS_F32 || EPI == EPI_F32_BIAS_F32_ACC)
               v = __float_as_uint(p.beta * static_cast<const float*>(p.bias)[n]);
             else if constexpr (EPI == EPI_S32_BIAS_S32_SCALE)
               v = __float_as_uint(p.beta *
@@ -509,6 +511,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     static_cast<uint8_t*>(p.C) + (static_cast<long long>(r) * p.ldc + col) * T::kOutBytes;
                 if constexpr (T::kOutS8)
                   *reinterpret_cast<int8_t*>(dst) = static_cast<int8_t>(static_cast<int>(o));
+                else if constexpr (T::kAddToC)
+                  *reinterpret_cast<float*>(dst) = *reinterpret_cast<const float*>(dst) + __uint_as_float(o);
                 else
                   *reinterpret_cast<uint32_t*>(dst) = o;
               }
@@ -573,10 +577,26 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int r = row0 + i * 4 + sub;
           rp[i] = r < p.M ? row_ptr(r) + piece * 16 : nullptr;
         }
+        // EPI_F32_BIAS_F32_ACC: the values of C this lane adds to, fetched one chunk ahead of their use
+        uint4 held[8];
+        auto fetch_c = [&](int c, uint4 (&dst)[8]) {
+          const bool in_range = n0 + c * 32 + piece * 4 < p.N;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = (in_range && rp[i] != nullptr) ? *reinterpret_cast<const uint4*>(rp[i] + c * 128)
+                                                   : make_uint4(0, 0, 0, 0);
+        };
+        if constexpr (T::kAddToC) {
+          if (row0 < p.M && n0 < p.N) fetch_c(0, held);
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           if (n0 + c * 32 >= p.N) break;  // uniform over the CTA
           if (row0 >= p.M) break;  // no valid row in this warp (its patch may not exist: narrow A stages)
+          uint4 ahead[8];
+          if constexpr (T::kAddToC) {
+            if (c + 1 < BN / 32) fetch_c(c + 1, ahead);  // zeros beyond N
+          }
           uint32_t v[32];
           __syncwarp();
           tmem_ld_32x32(taddr + c * 32, v);
@@ -596,8 +616,20 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const bool col_ok = n0 + c * 32 + piece * 4 < p.N;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const uint4 o = *reinterpret_cast<const uint4*>(patch + (i * 4 + sub) * 144 + piece * 16);
+            uint4 o = *reinterpret_cast<const uint4*>(patch + (i * 4 + sub) * 144 + piece * 16);
+            if constexpr (T::kAddToC) {
+              o.x = __float_as_uint(__uint_as_float(held[i].x) + __uint_as_float(o.x));
+              o.y = __float_as_uint(__uint_as_float(held[i].y) + __uint_as_float(o.y));
+              o.z = __float_as_uint(__uint_as_float(held[i].z) + __uint_as_float(o.z));
+              o.w = __float_as_uint(__uint_as_float(held[i].w) + __uint_as_float(o.w));
+            }
             if (col_ok && rp[i] != nullptr) *reinterpret_cast<uint4*>(rp[i] + c * 128) = o;
+          }
+          if constexpr (T::kAddToC) {
+            if (c + 1 < BN / 32) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) held[i] = ahead[i];
+            }
           }
         }
       }
@@ -965,7 +997,12 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
                       g.epilogue == EPI_S8_ALPHA || g.epilogue == EPI_S8_BIAS_S8_VEC;
   const bool has_bias = g.epilogue == EPI_S8_BIAS_S8 || g.epilogue == EPI_S8_BIAS_S8_RELU ||
                         g.epilogue == EPI_F32_BIAS_F32 || g.epilogue == EPI_S32_BIAS_S32_ADD ||
-                        g.epilogue == EPI_S32_BIAS_S32_SCALE || g.epilogue == EPI_S8_BIAS_S8_VEC;
+                        g.epilogue == EPI_S32_BIAS_S32_SCALE || g.epilogue == EPI_S8_BIAS_S8_VEC ||
+                        g.epilogue == EPI_F32_BIAS_F32_ACC;
+  if (g.epilogue == EPI_F32_BIAS_F32_ACC && g.scatter_rows != 0) {
+    set_error("the epilogue that adds to C cannot scatter its output");
+    return TI_E_INVALID;
+  }
   if (g.epilogue == EPI_S8_BIAS_S8_VEC && (!g.alpha_vec || !g.beta_vec)) {
     set_error("the per-column epilogue needs alpha and beta vectors");
     return TI_E_INVALID;
@@ -1042,6 +1079,7 @@ int launch_gemm_i8(const GemmProblem& g, cudaStream_t stream) {
     case EPI_S8_ALPHA: return launch_bn<EPI_S8_ALPHA>(g, bn, pair, splits, stream);
     case EPI_S32_RAW: return launch_bn<EPI_S32_RAW>(g, bn, pair, splits, stream);
     case EPI_S8_BIAS_S8_VEC: return launch_bn<EPI_S8_BIAS_S8_VEC>(g, bn, pair, splits, stream);
+    case EPI_F32_BIAS_F32_ACC: return launch_bn<EPI_F32_BIAS_F32_ACC>(g, bn, pair, splits, stream);
   }
   set_error("unknown epilogue %d", g.epilogue);
   return TI_E_INVALID;

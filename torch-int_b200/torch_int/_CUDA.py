@@ -120,16 +120,18 @@ if _c_abi_version() != 1:
     raise ImportError("torch_int._CUDA: libtorch_int_b200.so has an unexpected ABI version")
 
 EPI_S8_BIAS_S8, EPI_S8_BIAS_S8_RELU, EPI_F32_BIAS_F32, EPI_S32_BIAS_S32_ADD, \
-    EPI_S32_BIAS_S32_SCALE, EPI_F32_ALPHA, EPI_S8_ALPHA, EPI_S32_RAW, EPI_S8_BIAS_S8_VEC = range(9)
+    EPI_S32_BIAS_S32_SCALE, EPI_F32_ALPHA, EPI_S8_ALPHA, EPI_S32_RAW, EPI_S8_BIAS_S8_VEC, \
+    EPI_F32_BIAS_F32_ACC = range(10)
 _EPI_OUT_DTYPE = {
     EPI_S8_BIAS_S8: torch.int8, EPI_S8_BIAS_S8_RELU: torch.int8, EPI_F32_BIAS_F32: torch.float32,
     EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32,
     EPI_F32_ALPHA: torch.float32, EPI_S8_ALPHA: torch.int8, EPI_S32_RAW: torch.int32,
-    EPI_S8_BIAS_S8_VEC: torch.int8,
+    EPI_S8_BIAS_S8_VEC: torch.int8, EPI_F32_BIAS_F32_ACC: torch.float32,
 }
 _EPI_BIAS_DTYPE = {
     EPI_S8_BIAS_S8: torch.int8, EPI_S8_BIAS_S8_RELU: torch.int8, EPI_F32_BIAS_F32: torch.float32,
     EPI_S32_BIAS_S32_ADD: torch.int32, EPI_S32_BIAS_S32_SCALE: torch.int32, EPI_S8_BIAS_S8_VEC: torch.int8,
+    EPI_F32_BIAS_F32_ACC: torch.float32,
 }
 
 

@@ -68,6 +68,7 @@ class Int8OPTConfig:
 # TI_TP_CHECK_EVERY_PASS=1: read the kernels' status word (a device synchronisation and one small
 # collective) after EVERY tensor-parallel forward pass, not only after the first one of a workspace.
 _CHECK_EVERY_PASS = os.environ.get("TI_TP_CHECK_EVERY_PASS", "0") == "1"
+_RESIDUAL_IN_GEMM_MIN_ROWS = 128  # below this the GEMMs split K and reduce in scratch: the row kernel keeps the add
 
 
 def _round_up(v, m):
@@ -328,6 +329,10 @@ class Int8OPTDecoderLayer(nn.Module):
         self.self_attn_layer_norm = LayerNormQ(embed_dim)
         self.fc1 = W8A8B8O8LinearReLU(embed_dim, self.local_ffn)       # column-parallel
         self.fc2 = W8A8BFP32OFP32Linear(self.local_ffn, embed_dim)     # row-parallel
+        # Prefill on one GPU: out_proj and fc2 add their output to the fp32 residual in the GEMM epilogue
+        # (TI_RESIDUAL_IN_GEMM=0: the int32 products go through the fused residual/LayerNorm row kernel
+        # instead; same results bit for bit)
+        self.residual_in_gemm = os.environ.get("TI_RESIDUAL_IN_GEMM", "1") != "0"
         self.final_layer_norm = LayerNormQ(embed_dim)
 
     @staticmethod
@@ -347,12 +352,34 @@ class Int8OPTDecoderLayer(nn.Module):
     # ------------------------------------------------------------------ fast path
     @torch.no_grad()
     def forward_fused(self, residual, hidden_int8, cache, layer_idx, past_len, mask, next_ln: Optional[LayerNormQ],
-                      decode: bool = False):
+                      decode: bool = False, inplace: bool = False):
         """residual fp [B,T,E], hidden_int8 = LayerNormQ(residual) -> (new residual,
         int8 input of the next layer or None).  `next_ln` is the next layer's
-        self_attn_layer_norm (None after the last layer)."""
+        self_attn_layer_norm (None after the last layer).  `inplace`: the caller owns `residual` and lets
+        it be updated in place, as the reference's layer does (opt.py:281,289)."""
         shape = residual.shape
         attn = self.self_attn
+        if (inplace and self.residual_in_gemm and not decode and self.tp.size == 1 and residual.dtype == torch.float32
+                and residual.is_contiguous() and residual.numel() // self.embed_dim > _RESIDUAL_IN_GEMM_MIN_ROWS):
+            # Prefill on one GPU with an fp32 residual stream: out_proj and fc2 add fma(a, acc, bias) to the
+            # residual in their epilogues (same arithmetic as the fused row kernel below), and the row kernel
+            # only normalises and quantises: the int32 products never travel through HBM.
+            e = self.embed_dim
+            res2d = residual.view(-1, e)
+            ctx = attn.forward_fused(hidden_int8, cache, layer_idx, past_len, mask, context_only=True)
+            ctx2d = ctx.view(-1, attn.local_dim)
+            C.gemm_i8_ex(ctx2d, attn.out_proj.weight, res2d, attn.out_proj.bias, epilogue=C.EPI_F32_BIAS_F32_ACC,
+                         m=res2d.shape[0], n=e, k=attn.local_dim, lda=attn.local_dim, ldb=attn.local_dim, ldc=e,
+                         alpha=attn.out_proj._scalar("a"), beta=1.0)
+            ln = self.final_layer_norm
+            h8 = self.fc1._op(C.layernorm_q(res2d, ln.weight, ln.bias, ln.eps))
+            C.gemm_i8_ex(h8, self.fc2.weight, res2d, self.fc2.bias, epilogue=C.EPI_F32_BIAS_F32_ACC,
+                         m=res2d.shape[0], n=e, k=self.local_ffn, lda=self.local_ffn, ldb=self.local_ffn, ldc=e,
+                         alpha=self.fc2._scalar("a"), beta=1.0)
+            del h8
+            if next_ln is None:
+                return residual, None
+            return residual, C.layernorm_q(residual, next_ln.weight, next_ln.bias, next_ln.eps)
         acc = attn.forward_fused(hidden_int8, cache, layer_idx, past_len, mask, decode=decode)
         acc = self.tp.all_reduce_int32(acc)
         ln = self.final_layer_norm
@@ -706,6 +733,7 @@ class Int8OPTDecoder(nn.Module):
                 residual = layer(residual, attention_mask=ref_mask)[0]
         else:
             residual = hidden.to(self._stream_dtype(hidden)).contiguous()
+            owned = True  # `hidden` is this call's own sum of embeddings: the layers may update it in place
             chunks = self.tp.plan_chunks(bsz, tgt_len) if self.tp.size > 1 else 0
             if chunks:
                 residual = self._layers_pipelined(residual, cache, past_len, mask, chunks)
@@ -715,7 +743,8 @@ class Int8OPTDecoder(nn.Module):
                 n = len(self.layers)
                 for i, layer in enumerate(self.layers):
                     next_ln = self.layers[i + 1].self_attn_layer_norm if i + 1 < n else None
-                    residual, h8 = layer.forward_fused(residual, h8, cache, i, past_len, mask, next_ln)
+                    residual, h8 = layer.forward_fused(residual, h8, cache, i, past_len, mask, next_ln,
+                                                       inplace=owned)
             if cache is not None:
                 cache.set_length(src_len)
             residual = residual.to(hidden.dtype)
